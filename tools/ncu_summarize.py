@@ -2,7 +2,7 @@
 
   launch list  : ncu --metrics gpu__time_duration.sum --clock-control none -c N --csv --log-file L.csv <cmd>
                  python tools/ncu_summarize.py launches L.csv > profiles/<round>_launch_list_summary.txt
-  full capture : ncu --set full --clock-control none --import-source on -k regex:<kernels> -o R <cmd>
+  full capture : ncu --set full --clock-control none -k regex:<kernels> -o R <cmd>
                  ncu -i R.ncu-rep --page raw --csv > R.csv ; python tools/ncu_summarize.py full R.csv > profiles/<round>_ncu_full_metrics.txt
 (per-launch times under ncu are cold-cache and serialised: read the SHARES, not the absolutes — B200_PROFILING.md)"""
 import collections
