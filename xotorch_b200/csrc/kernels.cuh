@@ -51,7 +51,7 @@ __device__ __forceinline__ void fence_mbar_init() {
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
-// TMA 1-D bulk copy global -> shared, completion counted on an mbarrier (SASS: UBLKCP).
+// TMA 1-D bulk copy global -> shared, completion counted on an mbarrier.
 __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar,
                                          uint64_t policy) {
   asm volatile(
