@@ -1,0 +1,128 @@
+/*
+ * xotb200_lm.h — C ABI of libxotb200_lm.so: the layered-model engine of xotorch_b200 (sm_100a).
+ *
+ * libxotb200.so (xotb200.h) runs Llama-style shards through one persistent kernel.  This library runs decoders that are given as
+ * a LIST of layers — each a token mixer and an optional feed-forward between grouped RMS norms — where the mixers differ from
+ * layer to layer and keep different per-request state:
+ *   XOTB200_LM_MIX_LATENT_ATTN  attention over a compressed (latent) key/value row per token + one rotated key part shared by
+ *                               all heads; options: query through a normed latent, rotation layout, sliding window, output gate;
+ *                               state = the paged latent cache;
+ *   XOTB200_LM_MIX_DELTA_RULE   generalised delta-rule recurrence with per-channel decay and removal rate;
+ *                               state = one fp32 matrix per head, request and layer.
+ * Every size and constant of a layer is a field of xotb200_lm_layer, so a model family is a table of layers, not code.
+ *
+ * Serving model: requests live in SLOTS (0 .. max_requests-1).  A step (xotb200_lm_step) takes a packed batch — for each
+ * participating slot its next n >= 1 tokens — appends them to the slot's cache / state and returns the logits of the rows asked
+ * for.  Prompts, portions of prompts and single decoded tokens are the same call.  The latent cache is PAGED: one pool of pages
+ * per attention layer, a page table per slot, pages handed out as a request grows and returned by xotb200_lm_clear_request.
+ *
+ * Conventions as in xotb200.h: 0 on success, negative XOTB200_E* on failure (message: xotb200_lm_last_error(), thread-local);
+ * host pointers are caller-owned; calls on one engine are serialised by the caller.
+ */
+#ifndef XOTB200_LM_H
+#define XOTB200_LM_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#ifndef XOTB200_OK
+#define XOTB200_OK 0
+#define XOTB200_EINVAL (-1)
+#define XOTB200_ECUDA (-2)
+#define XOTB200_EIO (-3)
+#define XOTB200_ESTRICT (-4)
+#endif
+
+#define XOTB200_LM_DTYPE_BF16 0 /* weights, GEMM inputs and latent cache in bfloat16; fp32 accumulation, residual, norms, state */
+#define XOTB200_LM_DTYPE_F32 2  /* everything in true fp32 (FMA products, no reduced-precision matrix mode)                       */
+
+#define XOTB200_LM_MIX_LATENT_ATTN 0
+#define XOTB200_LM_MIX_DELTA_RULE 1
+
+#define XOTB200_LM_ROT_INTERLEAVED 0 /* pairs (2i, 2i+1)        */
+#define XOTB200_LM_ROT_HALF 1        /* pairs (i, i + dims / 2) */
+
+typedef struct xotb200_lm_layer {
+  int32_t mixer;      /* XOTB200_LM_MIX_*                                                                   */
+  int32_t heads;
+  int32_t dim;        /* latent attention: unrotated query/key size per head; delta rule: key size per head  */
+  int32_t vdim;       /* value size per head (delta rule: = dim)                                              */
+  int32_t rot_dim;    /* latent attention: size of the rotated query part / shared key part                   */
+  int32_t kv_rank;    /* latent attention: latent size                                                        */
+  int32_t q_rank;     /* latent attention: > 0 = queries through a normed latent of this size, 0 = direct     */
+  int32_t rot_dims;   /* how many leading entries of the rotated part are turned (<= rot_dim, even)           */
+  int32_t rot_layout; /* XOTB200_LM_ROT_*                                                                     */
+  int32_t window;     /* > 0: a query at position i sees i - window < j <= i; 0: every j <= i                 */
+  int32_t out_gate;   /* latent attention: 1 = one sigmoid gate per head on the mixer output                  */
+  int32_t low_rank;   /* delta rule: inner size of the decay branch                                           */
+  int32_t ff;         /* feed-forward inner size (relu^2 between up and down); 0 = the layer has none         */
+  float rot_base;
+  float scale;        /* score scale                                                                          */
+} xotb200_lm_layer;
+
+typedef struct xotb200_lm_cfg {
+  int32_t n_layers;    /* of the whole model                                   */
+  int32_t start_layer; /* inclusive layer range this engine runs (a shard)     */
+  int32_t end_layer;
+  int32_t width;
+  int32_t vocab;
+  int32_t norm_groups;
+  int32_t dtype;       /* XOTB200_LM_DTYPE_*                                   */
+  float norm_eps;
+} xotb200_lm_cfg;
+
+typedef struct xotb200_lm xotb200_lm;
+
+const char* xotb200_lm_last_error(void);
+const char* xotb200_lm_version(void);
+
+/* `layers` has cfg->n_layers entries (the engine keeps those of its range). */
+int xotb200_lm_create(const xotb200_lm_cfg* cfg, const xotb200_lm_layer* layers, int device, xotb200_lm** out);
+int xotb200_lm_destroy(xotb200_lm* e);
+
+/* Weights.  Tensor names: embed, head, final.norm, l<i>.norm1 / norm1b / norm2 / norm2b, l<i>.mix.<t>, l<i>.mlp.up / down with
+ * <t> in {dq, dq.norm, uq | q, dkv, dkv.norm, uk, uv, g, o} or {r, k, v, g, a, a.b, w1, w2, w0, norm, o}; linear weights [out, in].
+ * xotb200_lm_load_dir reads every *.safetensors of the directory (BF16 tensors) and is STRICT: a tensor of this shard that is
+ * missing, has another shape or dtype, or an unknown tensor of an owned layer, is an error. */
+int xotb200_lm_load_dir(xotb200_lm* e, const char* dir);
+/* one tensor from host memory as bf16 bit patterns; returns 1 when the tensor belongs to another shard (ignored) */
+int xotb200_lm_load_tensor(xotb200_lm* e, const char* name, const void* bf16_bits, const int64_t* shape, int ndim);
+int xotb200_lm_check_loaded(xotb200_lm* e);
+
+/* Request state: (re)creates the cache for at most max_requests live requests holding at most max_tokens tokens together.
+ * page_size tokens per page (0 = 64).  All slots start empty. */
+int xotb200_lm_begin(xotb200_lm* e, int max_tokens, int max_requests, int page_size);
+/* Empty a slot: its pages return to the pool, its recurrent states are zeroed, its length becomes 0. */
+int xotb200_lm_clear_request(xotb200_lm* e, int slot);
+int xotb200_lm_request_len(xotb200_lm* e, int slot, int* len);
+
+/* The step.  n_seq requests; request i is slot slots[i] and brings counts[i] >= 1 rows, which continue it at its current length.
+ * First shard: tokens[sum counts] (int32 ids); other shards: hidden_f32[sum counts, width] (the fp32 residual stream).
+ * want_rows[n_want]: indices into the packed rows whose output is asked for.
+ *   last shard : logits_f32[n_want, vocab] and/or argmax_i32[n_want] (lowest-index argmax) — either may be NULL;
+ *   other shards: hidden_out_f32[sum counts, width] (want_rows ignored).
+ * A slot may appear once per step.  Fails without touching any state when the pool has too few free pages. */
+int xotb200_lm_step(xotb200_lm* e, int n_seq, const int32_t* slots, const int32_t* counts, const int32_t* tokens,
+                    const float* hidden_f32, const int32_t* want_rows, int n_want, float* logits_f32, int32_t* argmax_i32,
+                    float* hidden_out_f32);
+
+/* Debug / tests: the fp32 residual stream after every layer of the most recent step is kept when enabled (trace = 1) and copied
+ * out as [local layers, rows, width]. */
+int xotb200_lm_set_trace(xotb200_lm* e, int on);
+int xotb200_lm_read_trace(xotb200_lm* e, float* out, int64_t n_floats);
+/* Projection kernel choice: 0 = automatic (<= 8 rows: the one-warp-per-output decode kernel, else tiles), 1 = always tiles. */
+int xotb200_lm_set_gemm_mode(xotb200_lm* e, int mode);
+
+int xotb200_lm_kernel_launches(xotb200_lm* e, int64_t* count);
+int xotb200_lm_weight_bytes(xotb200_lm* e, int64_t* bytes);
+int xotb200_lm_cache_stats(xotb200_lm* e, int* pages_total, int* pages_free, int* page_size);
+/* device time (CUDA events) of the most recent step, ms */
+int xotb200_lm_last_step_ms(xotb200_lm* e, float* ms);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* XOTB200_LM_H */

@@ -97,6 +97,85 @@ def load(path: os.PathLike | None = None) -> C.CDLL:
   return lib
 
 
+# ---- libxotb200_lm.so: the layered-model engine (include/xotb200_lm.h) --------------------------------------------------
+LM_LIB_PATH = Path(__file__).resolve().parent / "lib" / "libxotb200_lm.so"
+LM_DTYPE_BF16, LM_DTYPE_F32 = 0, 2
+LM_MIX_LATENT_ATTN, LM_MIX_DELTA_RULE = 0, 1
+LM_ROT_INTERLEAVED, LM_ROT_HALF = 0, 1
+
+
+class LmLayer(C.Structure):
+  """xotb200_lm_layer: one layer of a layered model (mixer kind, its sizes and constants, feed-forward size)"""
+  _fields_ = [
+    ("mixer", C.c_int32), ("heads", C.c_int32), ("dim", C.c_int32), ("vdim", C.c_int32), ("rot_dim", C.c_int32),
+    ("kv_rank", C.c_int32), ("q_rank", C.c_int32), ("rot_dims", C.c_int32), ("rot_layout", C.c_int32), ("window", C.c_int32),
+    ("out_gate", C.c_int32), ("low_rank", C.c_int32), ("ff", C.c_int32), ("rot_base", C.c_float), ("scale", C.c_float),
+  ]
+
+
+class LmCfg(C.Structure):
+  _fields_ = [
+    ("n_layers", C.c_int32), ("start_layer", C.c_int32), ("end_layer", C.c_int32), ("width", C.c_int32), ("vocab", C.c_int32),
+    ("norm_groups", C.c_int32), ("dtype", C.c_int32), ("norm_eps", C.c_float),
+  ]
+
+
+_I32P = C.POINTER(C.c_int32)
+_LM_SIGS = {
+  "xotb200_lm_last_error": (C.c_char_p, []),
+  "xotb200_lm_version": (C.c_char_p, []),
+  "xotb200_lm_create": (C.c_int, [C.POINTER(LmCfg), C.POINTER(LmLayer), C.c_int, C.POINTER(C.c_void_p)]),
+  "xotb200_lm_destroy": (C.c_int, [C.c_void_p]),
+  "xotb200_lm_load_dir": (C.c_int, [C.c_void_p, C.c_char_p]),
+  "xotb200_lm_load_tensor": (C.c_int, [C.c_void_p, C.c_char_p, C.c_void_p, C.POINTER(C.c_int64), C.c_int]),
+  "xotb200_lm_check_loaded": (C.c_int, [C.c_void_p]),
+  "xotb200_lm_begin": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int]),
+  "xotb200_lm_clear_request": (C.c_int, [C.c_void_p, C.c_int]),
+  "xotb200_lm_request_len": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_int)]),
+  "xotb200_lm_step": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p,
+                                C.c_void_p, C.c_void_p]),
+  "xotb200_lm_set_trace": (C.c_int, [C.c_void_p, C.c_int]),
+  "xotb200_lm_read_trace": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64]),
+  "xotb200_lm_set_gemm_mode": (C.c_int, [C.c_void_p, C.c_int]),
+  "xotb200_lm_kernel_launches": (C.c_int, [C.c_void_p, C.POINTER(C.c_int64)]),
+  "xotb200_lm_weight_bytes": (C.c_int, [C.c_void_p, C.POINTER(C.c_int64)]),
+  "xotb200_lm_cache_stats": (C.c_int, [C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+  "xotb200_lm_last_step_ms": (C.c_int, [C.c_void_p, C.POINTER(C.c_float)]),
+}
+LM_EXPORTED_SYMBOLS = tuple(_LM_SIGS.keys())
+_lm_lib = None
+
+
+def load_lm(path: os.PathLike | None = None, build: bool = True) -> C.CDLL:
+  """dlopen libxotb200_lm.so (once).  In a checkout that has not been built yet the library is compiled first — only this one
+  (`make lm`, a few seconds of nvcc), not the shard engine's persistent kernels.  Raises if it cannot be had: no CPU fallback."""
+  global _lm_lib
+  if _lm_lib is not None and path is None:
+    return _lm_lib
+  p = Path(path) if path else Path(os.environ.get("XOTB200_LM_LIB", LM_LIB_PATH))
+  if not p.exists() and build and path is None and "XOTB200_LM_LIB" not in os.environ:
+    import subprocess
+    src = Path(__file__).resolve().parent / "csrc"
+    r = subprocess.run(["make", "-C", str(src), "lm"], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if r.returncode != 0:
+      raise ImportError(f"building {p} failed:\n{r.stdout[-4000:]}")
+  if not p.exists():
+    raise ImportError(f"{p} not found: build it with `make -C xotorch_b200/csrc lm` — xotorch_b200 has no CPU fallback")
+  lib = C.CDLL(str(p))
+  for name, (res, args) in _LM_SIGS.items():
+    fn = getattr(lib, name)
+    fn.restype, fn.argtypes = res, args
+  if path is None:
+    _lm_lib = lib
+  return lib
+
+
+def check_lm(rc: int) -> int:
+  if rc < 0:
+    raise XotB200Error(rc, load_lm().xotb200_lm_last_error().decode("utf-8", "replace"))
+  return rc
+
+
 def check(rc: int) -> int:
   if rc < 0:
     raise XotB200Error(rc, load().xotb200_last_error().decode("utf-8", "replace"))

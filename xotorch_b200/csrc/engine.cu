@@ -39,6 +39,7 @@
 #include "kernels.cuh"
 #include "megakernel.cuh"
 #include "prefill_tc.cuh"
+#include "st_header.h"
 
 // Decode GEMV inner loop: 1 = mma.sync tensor-core path (default), 0 = the round-1 packed-FFMA2 loop (kept for A/B builds:
 // make EXTRA=-DXB_GEMV_MMA=0).  XB_TILE_STAMPS=1 adds per-tile timestamps to the debug timeline (tools/quick_bench.py).
@@ -751,78 +752,6 @@ static int prefill_tc(xotb200_engine* e, int n_tokens, int pos0, cudaStream_t st
   // the residual stream of the last position is what xotb200_post_to_next hands to the next shard
   CK(cudaMemcpyAsync(e->x, e->tc_x + (size_t)((n_tokens - 1) % TC_CHUNK) * D, (size_t)D * 2, cudaMemcpyDeviceToDevice, st));
   return 0;
-}
-
-// --------------------------------------------------------------------------------------------------------------
-// minimal JSON (safetensors header) parser
-// --------------------------------------------------------------------------------------------------------------
-struct StEntry {
-  std::string dtype;
-  std::vector<int64_t> shape;
-  int64_t begin = 0, end = 0;
-};
-struct JsonP {
-  const char* p;
-  const char* e;
-  bool ok = true;
-  void ws() { while (p < e && (*p == ' ' || *p == '\n' || *p == '\t' || *p == '\r')) ++p; }
-  bool eat(char c) { ws(); if (p < e && *p == c) { ++p; return true; } return false; }
-  std::string str() {
-    ws();
-    std::string s;
-    if (p >= e || *p != '"') { ok = false; return s; }
-    ++p;
-    while (p < e && *p != '"') {
-      if (*p == '\\' && p + 1 < e) { ++p; }
-      s.push_back(*p++);
-    }
-    if (p < e) ++p; else ok = false;
-    return s;
-  }
-  int64_t num() {
-    ws();
-    char* q = nullptr;
-    long long v = strtoll(p, &q, 10);
-    if (q == p) ok = false;
-    p = q;
-    return v;
-  }
-  void skip() {  // skip any value
-    ws();
-    if (p >= e) { ok = false; return; }
-    if (*p == '"') { str(); return; }
-    if (*p == '{') { ++p; if (eat('}')) return; do { str(); if (!eat(':')) { ok = false; return; } skip(); } while (ok && eat(',')); if (!eat('}')) ok = false; return; }
-    if (*p == '[') { ++p; if (eat(']')) return; do { skip(); } while (ok && eat(',')); if (!eat(']')) ok = false; return; }
-    while (p < e && *p != ',' && *p != '}' && *p != ']') ++p;
-  }
-};
-
-static bool parse_st_header(const char* s, size_t n, std::map<std::string, StEntry>& out) {
-  JsonP j{s, s + n};
-  if (!j.eat('{')) return false;
-  if (j.eat('}')) return true;
-  do {
-    std::string name = j.str();
-    if (!j.ok || !j.eat(':')) return false;
-    if (name == "__metadata__") { j.skip(); continue; }
-    if (!j.eat('{')) return false;
-    StEntry en;
-    do {
-      std::string k = j.str();
-      if (!j.eat(':')) return false;
-      if (k == "dtype") en.dtype = j.str();
-      else if (k == "shape") {
-        if (!j.eat('[')) return false;
-        if (!j.eat(']')) { do { en.shape.push_back(j.num()); } while (j.eat(',')); if (!j.eat(']')) return false; }
-      } else if (k == "data_offsets") {
-        if (!j.eat('[')) return false;
-        en.begin = j.num(); if (!j.eat(',')) return false; en.end = j.num(); if (!j.eat(']')) return false;
-      } else j.skip();
-    } while (j.ok && j.eat(','));
-    if (!j.eat('}')) return false;
-    out[name] = en;
-  } while (j.ok && j.eat(','));
-  return j.ok && j.eat('}');
 }
 
 // --------------------------------------------------------------------------------------------------------------

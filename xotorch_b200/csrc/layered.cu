@@ -1,0 +1,885 @@
+// layered.cu — host side of libxotb200_lm.so (include/xotb200_lm.h): the layered-model engine.
+//
+//   model     : a table of layers (xotb200_lm_layer); weights in ONE blob of T (bf16 or fp32), input projections of a mixer that
+//               read the same normed input are stored as one concatenated matrix so they are one product;
+//   loader    : strict safetensors reader (mmap -> device staging -> widen/copy kernel into the blob);
+//   state     : paged latent cache (one pool per attention layer, page table per slot, host free list) + fp32 recurrent states
+//               per slot; slots are emptied and reused, pages return to the pool;
+//   step      : a packed batch of rows through the layers on one stream (kernels in layered_kernels.cuh), logits / argmax of the
+//               wanted rows back to the host.
+#include <cuda_runtime.h>
+#include <dirent.h>
+#include <fcntl.h>
+#include <math.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+#include <sys/mman.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
+#include <algorithm>
+#include <map>
+#include <string>
+#include <vector>
+
+#include "../../include/xotb200_lm.h"
+#include "layered_kernels.cuh"
+#include "st_header.h"
+
+using namespace xl;
+
+static thread_local char g_err[1024] = "";
+static void set_err(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+#define CK(call)                                                                           \
+  do {                                                                                     \
+    cudaError_t _e = (call);                                                               \
+    if (_e != cudaSuccess) {                                                               \
+      set_err("%s failed: %s (%s:%d)", #call, cudaGetErrorString(_e), __FILE__, __LINE__); \
+      return XOTB200_ECUDA;                                                                \
+    }                                                                                      \
+  } while (0)
+#define REQUIRE(cond, ...)   \
+  do {                       \
+    if (!(cond)) {           \
+      set_err(__VA_ARGS__);  \
+      return XOTB200_EINVAL; \
+    }                        \
+  } while (0)
+#define TRY(call)           \
+  do {                      \
+    int _r = (call);        \
+    if (_r < 0) return _r;  \
+  } while (0)
+
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+static int cdiv(long a, long b) { return (int)((a + b - 1) / b); }
+
+// where a tensor of the file goes: rows [row_off, row_off + rows) of a [*, cols] matrix in the blob
+struct Dest {
+  size_t elem_off;   // element offset of the matrix in the blob
+  int rows, cols, row_off;
+  bool loaded;
+};
+
+struct LmLayer {
+  xotb200_lm_layer s;
+  size_t norm1, norm1b, norm2, norm2b;                 // element offsets into the blob
+  size_t w_in;                                         // concatenated input projections [n_in, D]
+  int n_in;
+  int c_q, c_kv, c_g;                                  // latent attention: columns of the projection output
+  size_t dq_norm, uq, dkv_norm, uk, uv, wo;
+  int c_r, c_k, c_v, c_a, c_w1;                        // delta rule: columns (gate shares c_g)
+  size_t w2, w0, a_b, onorm;
+  size_t up, down;
+  float* freqs = nullptr;                              // [rot_dims / 2] fp32 on the device
+  void* pool = nullptr;                                // latent pool [n_pages * P, kv_rank + rot_dim] of T
+  size_t state_off = 0;                                // delta rule: float offset of this layer's state inside a slot's block
+};
+
+struct xotb200_lm {
+  xotb200_lm_cfg cfg;
+  std::vector<LmLayer> layers;                         // local layers
+  int device = 0, sm_count = 148;
+  bool first = false, last = false;
+  size_t esz = 2;
+  cudaStream_t stream = nullptr;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  char* blob = nullptr;
+  size_t blob_elems = 0;
+  size_t embed = 0, final_norm = 0, head = 0;
+  std::map<std::string, Dest> dests;
+  // request state
+  int max_requests = 0, page_size = 0, n_pages = 0, pages_per_slot = 0;
+  std::vector<int> free_pages, slot_len, slot_pages;
+  int* h_table = nullptr;                              // pinned [max_requests, pages_per_slot]
+  int* d_table = nullptr;
+  float* state = nullptr;                              // [max_requests][state_floats]
+  size_t state_floats = 0;
+  // per-step staging
+  int* h_stage = nullptr;
+  int* d_stage = nullptr;
+  size_t stage_cap = 0;
+  // scratch (rows capacity m_cap)
+  int m_cap = 0, want_cap = 0;
+  float *x = nullptr, *y = nullptr, *proj = nullptr, *qraw = nullptr, *qfull = nullptr, *wlog = nullptr, *oraw = nullptr, *logits = nullptr;
+  void *h = nullptr, *cqn = nullptr, *qn = nullptr, *olat = nullptr, *oh = nullptr, *act = nullptr, *th = nullptr, *hw = nullptr;
+  int* d_argmax = nullptr;
+  float* h_out = nullptr;                              // pinned staging for results
+  size_t h_out_cap = 0;
+  int max_in = 0, max_q = 0, max_qfull = 0, max_qr = 0, max_hdn = 0, max_olat = 0, max_oh = 0, max_ff = 0, max_hd = 0, max_lr = 0;
+  bool trace = false;
+  float* trace_buf = nullptr;
+  size_t trace_floats = 0, trace_cap = 0;
+  int gemm_mode = 0;
+  int64_t launches = 0;
+  float last_ms = 0.f;
+};
+
+template <typename T> static T* at(xotb200_lm* e, size_t off) { return reinterpret_cast<T*>(e->blob) + off; }
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// layout
+// ---------------------------------------------------------------------------------------------------------------------------
+static int build_layout(xotb200_lm* e, const xotb200_lm_layer* all) {
+  const int D = e->cfg.width, V = e->cfg.vocab;
+  size_t cur = 0;
+  const size_t al = 256 / e->esz;
+  auto take = [&](size_t n) { size_t o = cur; cur = align_up(cur + n, al); return o; };
+  auto dest = [&](const std::string& name, size_t off, int rows, int cols, int row_off) { e->dests[name] = Dest{off, rows, cols, row_off, false}; };
+  if (e->first) { e->embed = take((size_t)V * D); dest("embed", e->embed, V, D, 0); }
+  for (int li = e->cfg.start_layer; li <= e->cfg.end_layer; ++li) {
+    LmLayer L{};
+    L.s = all[li];
+    const xotb200_lm_layer& s = L.s;
+    const std::string p = "l" + std::to_string(li) + ".";
+    REQUIRE(s.heads >= 1 && s.dim >= 1, "layer %d: heads and dim must be positive", li);
+    L.norm1 = take(D); dest(p + "norm1", L.norm1, 1, D, 0);
+    L.norm1b = take(D); dest(p + "norm1b", L.norm1b, 1, D, 0);
+    if (s.mixer == XOTB200_LM_MIX_LATENT_ATTN) {
+      const int H = s.heads, dn = s.dim, dr = s.rot_dim, dv = s.vdim, R = s.kv_rank, HQ = H * (dn + dr);
+      REQUIRE(R >= 1 && R <= 512, "layer %d: kv_rank %d outside 1..512", li, R);
+      REQUIRE(dv >= 1 && dr >= 0 && s.rot_dims <= dr && s.rot_dims % 2 == 0 && s.rot_dims >= 0, "layer %d: bad rotation sizes", li);
+      REQUIRE(s.window >= 0, "layer %d: negative window", li);
+      const int nq = s.q_rank > 0 ? s.q_rank : HQ;
+      L.c_q = 0; L.c_kv = nq; L.c_g = nq + R + dr;
+      L.n_in = nq + R + dr + (s.out_gate ? H : 0);
+      L.w_in = take((size_t)L.n_in * D);
+      if (s.q_rank > 0) {
+        dest(p + "mix.dq", L.w_in, s.q_rank, D, 0);
+        L.dq_norm = take(s.q_rank); dest(p + "mix.dq.norm", L.dq_norm, 1, s.q_rank, 0);
+        L.uq = take((size_t)HQ * s.q_rank); dest(p + "mix.uq", L.uq, HQ, s.q_rank, 0);
+      } else {
+        dest(p + "mix.q", L.w_in, HQ, D, 0);
+      }
+      dest(p + "mix.dkv", L.w_in, R + dr, D, L.c_kv);
+      if (s.out_gate) dest(p + "mix.g", L.w_in, H, D, L.c_g);
+      L.dkv_norm = take(R); dest(p + "mix.dkv.norm", L.dkv_norm, 1, R, 0);
+      L.uk = take((size_t)H * dn * R); dest(p + "mix.uk", L.uk, H * dn, R, 0);
+      L.uv = take((size_t)H * dv * R); dest(p + "mix.uv", L.uv, H * dv, R, 0);
+      L.wo = take((size_t)D * H * dv); dest(p + "mix.o", L.wo, D, H * dv, 0);
+      e->max_q = std::max(e->max_q, HQ);
+      e->max_qfull = std::max(e->max_qfull, H * (R + dr));
+      e->max_qr = std::max(e->max_qr, s.q_rank);
+      e->max_hdn = std::max(e->max_hdn, H * dn);
+      e->max_olat = std::max(e->max_olat, H * R);
+      e->max_oh = std::max(e->max_oh, H * dv);
+    } else if (s.mixer == XOTB200_LM_MIX_DELTA_RULE) {
+      const int HD = s.heads * s.dim;
+      REQUIRE(s.vdim == s.dim, "layer %d: the delta rule uses one size for keys and values", li);
+      REQUIRE(s.dim <= 256, "layer %d: delta-rule head size %d above 256", li, s.dim);
+      REQUIRE(s.low_rank >= 1, "layer %d: the decay branch needs an inner size", li);
+      L.c_r = 0; L.c_k = HD; L.c_v = 2 * HD; L.c_g = 3 * HD; L.c_a = 4 * HD; L.c_w1 = 5 * HD;
+      L.n_in = 5 * HD + s.low_rank;
+      L.w_in = take((size_t)L.n_in * D);
+      dest(p + "mix.r", L.w_in, HD, D, L.c_r);
+      dest(p + "mix.k", L.w_in, HD, D, L.c_k);
+      dest(p + "mix.v", L.w_in, HD, D, L.c_v);
+      dest(p + "mix.g", L.w_in, HD, D, L.c_g);
+      dest(p + "mix.a", L.w_in, HD, D, L.c_a);
+      dest(p + "mix.w1", L.w_in, s.low_rank, D, L.c_w1);
+      L.w2 = take((size_t)HD * s.low_rank); dest(p + "mix.w2", L.w2, HD, s.low_rank, 0);
+      L.w0 = take(HD); dest(p + "mix.w0", L.w0, 1, HD, 0);
+      L.a_b = take(HD); dest(p + "mix.a.b", L.a_b, 1, HD, 0);
+      L.onorm = take(HD); dest(p + "mix.norm", L.onorm, 1, HD, 0);
+      L.wo = take((size_t)D * HD); dest(p + "mix.o", L.wo, D, HD, 0);
+      L.state_off = e->state_floats;
+      e->state_floats += (size_t)s.heads * s.dim * s.dim;
+      e->max_hd = std::max(e->max_hd, HD);
+      e->max_lr = std::max(e->max_lr, s.low_rank);
+      e->max_oh = std::max(e->max_oh, HD);
+    } else {
+      REQUIRE(false, "layer %d: unknown mixer kind %d", li, s.mixer);
+    }
+    e->max_in = std::max(e->max_in, L.n_in);
+    if (s.ff > 0) {
+      L.norm2 = take(D); dest(p + "norm2", L.norm2, 1, D, 0);
+      L.norm2b = take(D); dest(p + "norm2b", L.norm2b, 1, D, 0);
+      L.up = take((size_t)s.ff * D); dest(p + "mlp.up", L.up, s.ff, D, 0);
+      L.down = take((size_t)D * s.ff); dest(p + "mlp.down", L.down, D, s.ff, 0);
+      e->max_ff = std::max(e->max_ff, s.ff);
+    }
+    e->layers.push_back(L);
+  }
+  if (e->last) {
+    e->final_norm = take(D); dest("final.norm", e->final_norm, 1, D, 0);
+    e->head = take((size_t)V * D); dest("head", e->head, V, D, 0);
+  }
+  e->blob_elems = cur;
+  return 0;
+}
+
+static int upload_tensor(xotb200_lm* e, Dest& d, const void* host_bf16) {
+  const size_t n = (size_t)d.rows * d.cols;
+  bf16* tmp = nullptr;
+  CK(cudaMalloc(&tmp, n * 2));
+  cudaError_t er = cudaMemcpyAsync(tmp, host_bf16, n * 2, cudaMemcpyHostToDevice, e->stream);
+  if (er == cudaSuccess) {
+    const int grid = (int)std::min<size_t>(4096, (n + 255) / 256);
+    const size_t off = d.elem_off + (size_t)d.row_off * d.cols;
+    if (e->esz == 2) store_rows_kernel<bf16><<<grid, 256, 0, e->stream>>>(tmp, at<bf16>(e, off), n);
+    else store_rows_kernel<float><<<grid, 256, 0, e->stream>>>(tmp, at<float>(e, off), n);
+    er = cudaGetLastError();
+    e->launches++;
+  }
+  cudaError_t er2 = cudaStreamSynchronize(e->stream);
+  cudaFree(tmp);
+  CK(er);
+  CK(er2);
+  d.loaded = true;
+  return 0;
+}
+
+// does a tensor name belong to this shard? (so that an unknown name there is an error, and anything else is skipped)
+static bool owned_name(const xotb200_lm* e, const std::string& name) {
+  if (name == "embed") return e->first;
+  if (name == "head" || name == "final.norm") return e->last;
+  if (name.size() > 1 && name[0] == 'l' && isdigit((unsigned char)name[1])) {
+    const int li = atoi(name.c_str() + 1);
+    return li >= e->cfg.start_layer && li <= e->cfg.end_layer;
+  }
+  return true;   // not a name of this model family at all: strict
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// products
+// ---------------------------------------------------------------------------------------------------------------------------
+static const size_t GEMV_SMEM_MAX = 160 * 1024;
+
+template <typename K>
+static int opt_in_smem(K kernel, size_t bytes) {
+  if (bytes > 48 * 1024) CK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+  return 0;
+}
+
+template <typename TA, typename TB, typename TC, int EPI>
+static int product(xotb200_lm* e, const TA* A, long lda, long a_batch, const TB* B, long sbn, long sbk, long b_batch, TC* C, long ldc, long c_batch,
+                   int M, int N, int K, int batch) {
+  if (M == 0 || N == 0) return 0;
+  const size_t smem = (size_t)M * K * 4;
+  if (e->gemm_mode == 0 && M <= 8 && sbk == 1 && smem <= GEMV_SMEM_MAX) {
+    auto kern = gemv_rows_kernel<TA, TB, TC, EPI, 8>;
+    TRY(opt_in_smem(kern, smem));
+    const int blocks = std::max(1, std::min(cdiv(N, 8), e->sm_count * 4 / std::max(1, batch)));
+    kern<<<dim3(blocks, 1, batch), 256, smem, e->stream>>>(A, lda, a_batch, B, sbn, b_batch, C, ldc, c_batch, M, N, K);
+  } else {
+    gemm_tiled_kernel<TA, TB, TC, EPI><<<dim3(cdiv(N, 64), cdiv(M, 64), batch), 256, 0, e->stream>>>(A, lda, a_batch, B, sbn, sbk, b_batch, C, ldc,
+                                                                                                  c_batch, M, N, K);
+  }
+  CK(cudaGetLastError());
+  e->launches++;
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// scratch
+// ---------------------------------------------------------------------------------------------------------------------------
+template <typename P> static int regrow(P*& p, size_t bytes) {
+  if (p) { cudaFree(p); p = nullptr; }
+  if (bytes == 0) return 0;
+  CK(cudaMalloc(&p, bytes));
+  return 0;
+}
+
+static int ensure_scratch(xotb200_lm* e, int M, int n_want) {
+  const int D = e->cfg.width;
+  if (M > e->m_cap) {
+    const size_t m = (size_t)std::max(M, 64), z = e->esz;
+    TRY(regrow(e->x, m * D * 4));
+    TRY(regrow(e->y, m * D * 4));
+    TRY(regrow(e->proj, m * e->max_in * 4));
+    TRY(regrow(e->qraw, m * e->max_q * 4));
+    TRY(regrow(e->qfull, m * e->max_qfull * 4));
+    TRY(regrow(e->wlog, m * e->max_hd * 4));
+    TRY(regrow(e->oraw, m * e->max_hd * 4));
+    TRY(regrow(e->h, m * D * z));
+    TRY(regrow(e->cqn, m * e->max_qr * z));
+    TRY(regrow(e->qn, m * e->max_hdn * z));
+    TRY(regrow(e->olat, m * e->max_olat * z));
+    TRY(regrow(e->oh, m * e->max_oh * z));
+    TRY(regrow(e->act, m * e->max_ff * z));
+    TRY(regrow(e->th, m * e->max_lr * z));
+    e->m_cap = (int)m;
+    e->trace_cap = 0;
+  }
+  if (n_want > e->want_cap) {
+    const size_t w = (size_t)std::max(n_want, 16);
+    TRY(regrow(e->hw, w * D * e->esz));
+    TRY(regrow(e->logits, w * e->cfg.vocab * 4));
+    TRY(regrow(e->d_argmax, w * 4));
+    e->want_cap = (int)w;
+  }
+  if (e->trace && e->trace_cap < (size_t)e->layers.size() * e->m_cap * D) {
+    e->trace_cap = (size_t)e->layers.size() * e->m_cap * D;
+    TRY(regrow(e->trace_buf, e->trace_cap * 4));
+  }
+  return 0;
+}
+
+static int ensure_host_out(xotb200_lm* e, size_t floats) {
+  if (floats <= e->h_out_cap) return 0;
+  if (e->h_out) { cudaFreeHost(e->h_out); e->h_out = nullptr; }
+  CK(cudaHostAlloc(&e->h_out, floats * 4, cudaHostAllocDefault));
+  e->h_out_cap = floats;
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// the step
+// ---------------------------------------------------------------------------------------------------------------------------
+struct StepPlan {
+  int M = 0, n_seq = 0;
+  const int *tokens = nullptr, *row_slot = nullptr, *row_pos = nullptr, *want = nullptr;   // device
+  const Item* seqs = nullptr;
+  std::map<int, std::pair<const Item*, int>> items;   // rows per attention work item -> (device list, count)
+};
+
+template <typename T>
+static int attention_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
+  const xotb200_lm_layer& s = L.s;
+  const int D = e->cfg.width, M = sp.M, H = s.heads, dn = s.dim, dr = s.rot_dim, dv = s.vdim, R = s.kv_rank, HQ = H * (dn + dr);
+  const float eps = e->cfg.norm_eps;
+  T* h = static_cast<T*>(e->h);
+  // every projection that reads the normed input, as one product
+  TRY((product<T, T, float, 0>(e, h, D, 0, at<T>(e, L.w_in), D, 1, 0, e->proj, L.n_in, 0, M, L.n_in, D, 1)));
+  const float* qraw = e->proj;
+  int q_ld = L.n_in;
+  if (s.q_rank > 0) {
+    rmsnorm_cols_kernel<T><<<cdiv(M, 8), 256, 0, e->stream>>>(e->proj, L.n_in, L.c_q, s.q_rank, at<T>(e, L.dq_norm), static_cast<T*>(e->cqn), s.q_rank, M, eps);
+    CK(cudaGetLastError());
+    e->launches++;
+    TRY((product<T, T, float, 0>(e, static_cast<T*>(e->cqn), s.q_rank, 0, at<T>(e, L.uq), s.q_rank, 1, 0, e->qraw, HQ, 0, M, HQ, s.q_rank, 1)));
+    qraw = e->qraw;
+    q_ld = HQ;
+  }
+  const Paging pg{e->d_table, e->pages_per_slot, e->page_size};
+  latent_append_kernel<T><<<cdiv(M, 8), 256, 0, e->stream>>>(e->proj, L.n_in, L.c_kv, R, dr, at<T>(e, L.dkv_norm), eps, L.freqs, s.rot_dims, s.rot_layout,
+                                                             sp.row_slot, sp.row_pos, pg, static_cast<T*>(L.pool), M);
+  CK(cudaGetLastError());
+  query_split_kernel<T><<<cdiv((long)M * H, 8), 256, 0, e->stream>>>(qraw, q_ld, 0, H, dn, dr, R, L.freqs, s.rot_dims, s.rot_layout, sp.row_pos,
+                                                                      static_cast<T*>(e->qn), e->qfull, M);
+  CK(cudaGetLastError());
+  e->launches += 2;
+  // key absorption: qfull[m, h, 0:R] = sum_d qn[m, h, d] * W_uk[h * dn + d, :]
+  TRY((product<T, T, float, 0>(e, static_cast<T*>(e->qn), (long)H * dn, dn, at<T>(e, L.uk), 1, R, (long)dn * R, e->qfull, (long)H * (R + dr), R + dr, M, R,
+                               dn, H)));
+  {
+    const int qpi = std::max(1, 32 / H);
+    const auto& it = sp.items.at(qpi);
+    const int pairs = qpi * H, nw = std::min(32, pairs);
+    const size_t smem = ((size_t)32 * ((R + dr) | 1) + (size_t)nw * (R + dr)) * 4;
+    const float* gate = s.out_gate ? e->proj : nullptr;
+    const dim3 grid(it.second, cdiv(pairs, nw));
+#define LAUNCH_ATTN(NACC)                                                                                                                       \
+  do {                                                                                                                                          \
+    auto kern = latent_attention_kernel<T, NACC>;                                                                                               \
+    TRY(opt_in_smem(kern, smem));                                                                                                               \
+    kern<<<grid, nw * 32, smem, e->stream>>>(e->qfull, static_cast<const T*>(L.pool), pg, it.first, H, R, dr, s.scale, s.window, gate, L.n_in, \
+                                             L.c_g, static_cast<T*>(e->olat));                                                                  \
+  } while (0)
+    if (R <= 64) LAUNCH_ATTN(2);
+    else if (R <= 128) LAUNCH_ATTN(4);
+    else if (R <= 256) LAUNCH_ATTN(8);
+    else LAUNCH_ATTN(16);
+#undef LAUNCH_ATTN
+    CK(cudaGetLastError());
+    e->launches++;
+  }
+  // value expansion per head, then the output projection
+  TRY((product<T, T, T, 0>(e, static_cast<T*>(e->olat), (long)H * R, R, at<T>(e, L.uv), R, 1, (long)dv * R, static_cast<T*>(e->oh), (long)H * dv, dv, M, dv,
+                           R, H)));
+  TRY((product<T, T, float, 0>(e, static_cast<T*>(e->oh), (long)H * dv, 0, at<T>(e, L.wo), (long)H * dv, 1, 0, e->y, D, 0, M, D, H * dv, 1)));
+  return 0;
+}
+
+template <typename T, int KPT, int P>
+static int launch_delta(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
+  const xotb200_lm_layer& s = L.s;
+  constexpr int CPW = 32 / P, WARPS = 4;
+  const dim3 grid(sp.n_seq * s.heads, cdiv(s.vdim, WARPS * CPW));
+  delta_rule_kernel<T, KPT, P><<<grid, WARPS * 32, (size_t)8 * s.vdim * 4, e->stream>>>(
+      e->proj, L.n_in, L.c_r, L.c_k, L.c_v, L.c_a, e->wlog, at<T>(e, L.w0), at<T>(e, L.a_b), sp.seqs, s.heads, s.dim, s.vdim, e->state + L.state_off,
+      e->state_floats, e->oraw);
+  CK(cudaGetLastError());
+  e->launches++;
+  return 0;
+}
+
+template <typename T>
+static int delta_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
+  const xotb200_lm_layer& s = L.s;
+  const int D = e->cfg.width, M = sp.M, HD = s.heads * s.dim;
+  T* h = static_cast<T*>(e->h);
+  TRY((product<T, T, float, 0>(e, h, D, 0, at<T>(e, L.w_in), D, 1, 0, e->proj, L.n_in, 0, M, L.n_in, D, 1)));
+  tanh_cols_kernel<T><<<cdiv((long)M * s.low_rank, 256), 256, 0, e->stream>>>(e->proj, L.n_in, L.c_w1, s.low_rank, static_cast<T*>(e->th), M);
+  CK(cudaGetLastError());
+  e->launches++;
+  TRY((product<T, T, float, 0>(e, static_cast<T*>(e->th), s.low_rank, 0, at<T>(e, L.w2), s.low_rank, 1, 0, e->wlog, HD, 0, M, HD, s.low_rank, 1)));
+  if (s.dim <= 16) TRY((launch_delta<T, 16, 1>(e, L, sp)));
+  else if (s.dim <= 32) TRY((launch_delta<T, 16, 2>(e, L, sp)));
+  else if (s.dim <= 64) TRY((launch_delta<T, 16, 4>(e, L, sp)));
+  else if (s.dim <= 128) TRY((launch_delta<T, 16, 8>(e, L, sp)));
+  else TRY((launch_delta<T, 32, 8>(e, L, sp)));
+  head_norm_gate_kernel<T><<<cdiv((long)M * s.heads, 8), 256, 0, e->stream>>>(e->oraw, at<T>(e, L.onorm), e->proj, L.n_in, L.c_g, static_cast<T*>(e->oh), s.heads,
+                                                                               s.vdim, e->cfg.norm_eps, M);
+  CK(cudaGetLastError());
+  e->launches++;
+  TRY((product<T, T, float, 0>(e, static_cast<T*>(e->oh), HD, 0, at<T>(e, L.wo), HD, 1, 0, e->y, D, 0, M, D, HD, 1)));
+  return 0;
+}
+
+template <typename T>
+static int run_layers(xotb200_lm* e, const StepPlan& sp, int n_want) {
+  const int D = e->cfg.width, G = e->cfg.norm_groups, M = sp.M;
+  const float eps = e->cfg.norm_eps;
+  T* h = static_cast<T*>(e->h);
+  const float* pend_y = nullptr;
+  const T* pend_w = nullptr;
+  // x += groupnorm(pending sublayer output) * its post-norm weight;  h = groupnorm(x) * w_pre  (either half may be absent)
+  auto open = [&](const T* w_pre) -> int {
+    if (!pend_y && !w_pre) return 0;
+    residual_groupnorm_kernel<T><<<M, 128, 0, e->stream>>>(e->x, pend_y, pend_w, w_pre, w_pre ? h : nullptr, nullptr, D, G, eps);
+    CK(cudaGetLastError());
+    e->launches++;
+    pend_y = nullptr;
+    pend_w = nullptr;
+    return 0;
+  };
+  if (e->first) {
+    embed_rows_kernel<T><<<M, 128, 0, e->stream>>>(at<T>(e, e->embed), sp.tokens, e->x, D);
+    CK(cudaGetLastError());
+    e->launches++;
+  }
+  for (size_t li = 0; li < e->layers.size(); ++li) {
+    LmLayer& L = e->layers[li];
+    TRY(open(at<T>(e, L.norm1)));
+    if (L.s.mixer == XOTB200_LM_MIX_LATENT_ATTN) TRY(attention_layer<T>(e, L, sp));
+    else TRY(delta_layer<T>(e, L, sp));
+    pend_y = e->y;
+    pend_w = at<T>(e, L.norm1b);
+    if (L.s.ff > 0) {
+      TRY(open(at<T>(e, L.norm2)));
+      TRY((product<T, T, T, 1>(e, h, D, 0, at<T>(e, L.up), D, 1, 0, static_cast<T*>(e->act), L.s.ff, 0, M, L.s.ff, D, 1)));
+      TRY((product<T, T, float, 0>(e, static_cast<T*>(e->act), L.s.ff, 0, at<T>(e, L.down), L.s.ff, 1, 0, e->y, D, 0, M, D, L.s.ff, 1)));
+      pend_y = e->y;
+      pend_w = at<T>(e, L.norm2b);
+    }
+    if (e->trace) {
+      TRY(open(nullptr));
+      CK(cudaMemcpyAsync(e->trace_buf + li * (size_t)M * D, e->x, (size_t)M * D * 4, cudaMemcpyDeviceToDevice, e->stream));
+    }
+  }
+  TRY(open(nullptr));
+  if (e->trace) e->trace_floats = e->layers.size() * (size_t)M * D;
+  if (e->last && n_want > 0) {
+    T* hw = static_cast<T*>(e->hw);
+    residual_groupnorm_kernel<T><<<n_want, 128, 0, e->stream>>>(e->x, nullptr, nullptr, at<T>(e, e->final_norm), hw, sp.want, D, G, eps);
+    CK(cudaGetLastError());
+    e->launches++;
+    TRY((product<T, T, float, 0>(e, hw, D, 0, at<T>(e, e->head), D, 1, 0, e->logits, e->cfg.vocab, 0, n_want, e->cfg.vocab, D, 1)));
+    argmax_rows_kernel<<<n_want, 256, 0, e->stream>>>(e->logits, e->cfg.vocab, e->d_argmax);
+    CK(cudaGetLastError());
+    e->launches++;
+  }
+  return 0;
+}
+
+static void free_state(xotb200_lm* e) {
+  for (auto& L : e->layers)
+    if (L.pool) { cudaFree(L.pool); L.pool = nullptr; }
+  if (e->h_table) { cudaFreeHost(e->h_table); e->h_table = nullptr; }
+  if (e->d_table) { cudaFree(e->d_table); e->d_table = nullptr; }
+  if (e->state) { cudaFree(e->state); e->state = nullptr; }
+  e->max_requests = 0;
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// C ABI
+// ---------------------------------------------------------------------------------------------------------------------------
+extern "C" {
+
+const char* xotb200_lm_last_error(void) { return g_err; }
+const char* xotb200_lm_version(void) { return "xotb200_lm 0.1.0 sm_100a"; }
+
+int xotb200_lm_create(const xotb200_lm_cfg* cfg, const xotb200_lm_layer* layers, int device, xotb200_lm** out) {
+  REQUIRE(cfg && layers && out, "null argument");
+  REQUIRE(cfg->dtype == XOTB200_LM_DTYPE_BF16 || cfg->dtype == XOTB200_LM_DTYPE_F32, "dtype must be bf16 (0) or f32 (2), got %d", cfg->dtype);
+  REQUIRE(cfg->n_layers >= 1 && 0 <= cfg->start_layer && cfg->start_layer <= cfg->end_layer && cfg->end_layer < cfg->n_layers,
+          "bad layer range [%d, %d] of %d", cfg->start_layer, cfg->end_layer, cfg->n_layers);
+  REQUIRE(cfg->width >= 1 && cfg->vocab >= 1, "width and vocab must be positive");
+  REQUIRE(cfg->norm_groups >= 1 && cfg->width % cfg->norm_groups == 0, "width %d is not a multiple of norm_groups %d", cfg->width, cfg->norm_groups);
+  int ndev = 0;
+  CK(cudaGetDeviceCount(&ndev));
+  REQUIRE(device >= 0 && device < ndev, "device %d out of range (%d visible)", device, ndev);
+  CK(cudaSetDevice(device));
+  cudaDeviceProp prop;
+  CK(cudaGetDeviceProperties(&prop, device));
+  REQUIRE(prop.major == 10, "libxotb200_lm is sm_100a-only; device %d is sm_%d%d", device, prop.major, prop.minor);
+  xotb200_lm* e = new xotb200_lm();
+  e->cfg = *cfg;
+  e->device = device;
+  e->sm_count = prop.multiProcessorCount;
+  e->first = cfg->start_layer == 0;
+  e->last = cfg->end_layer == cfg->n_layers - 1;
+  e->esz = cfg->dtype == XOTB200_LM_DTYPE_F32 ? 4 : 2;
+  int rc = build_layout(e, layers);
+  if (rc < 0) { delete e; return rc; }
+  auto fail = [&](int code) { xotb200_lm_destroy(e); return code; };
+  if (cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking) != cudaSuccess || cudaEventCreate(&e->ev0) != cudaSuccess ||
+      cudaEventCreate(&e->ev1) != cudaSuccess || cudaMalloc(&e->blob, e->blob_elems * e->esz) != cudaSuccess) {
+    set_err("device allocation of %zu weight bytes failed: %s", e->blob_elems * e->esz, cudaGetErrorString(cudaGetLastError()));
+    return fail(XOTB200_ECUDA);
+  }
+  cudaMemsetAsync(e->blob, 0, e->blob_elems * e->esz, e->stream);
+  for (auto& L : e->layers) {
+    if (L.s.mixer != XOTB200_LM_MIX_LATENT_ATTN || L.s.rot_dims == 0) continue;
+    std::vector<float> f(L.s.rot_dims / 2);
+    for (int i = 0; i < L.s.rot_dims / 2; ++i) f[i] = (float)pow((double)L.s.rot_base, -2.0 * i / L.s.rot_dims);
+    if (cudaMalloc(&L.freqs, f.size() * 4) != cudaSuccess ||
+        cudaMemcpyAsync(L.freqs, f.data(), f.size() * 4, cudaMemcpyHostToDevice, e->stream) != cudaSuccess ||
+        cudaStreamSynchronize(e->stream) != cudaSuccess) {
+      set_err("rotation table allocation failed");
+      return fail(XOTB200_ECUDA);
+    }
+  }
+  cudaStreamSynchronize(e->stream);
+  *out = e;
+  return 0;
+}
+
+int xotb200_lm_destroy(xotb200_lm* e) {
+  if (!e) return 0;
+  cudaSetDevice(e->device);
+  if (e->stream) cudaStreamSynchronize(e->stream);
+  free_state(e);
+  for (auto& L : e->layers)
+    if (L.freqs) cudaFree(L.freqs);
+  void* ptrs[] = {e->blob, e->d_stage, e->x, e->y, e->proj, e->qraw, e->qfull, e->wlog, e->oraw, e->logits, e->h, e->cqn, e->qn, e->olat, e->oh, e->act,
+                  e->th, e->hw, e->d_argmax, e->trace_buf};
+  for (void* p : ptrs)
+    if (p) cudaFree(p);
+  if (e->h_stage) cudaFreeHost(e->h_stage);
+  if (e->h_out) cudaFreeHost(e->h_out);
+  if (e->ev0) cudaEventDestroy(e->ev0);
+  if (e->ev1) cudaEventDestroy(e->ev1);
+  if (e->stream) cudaStreamDestroy(e->stream);
+  delete e;
+  return 0;
+}
+
+int xotb200_lm_load_tensor(xotb200_lm* e, const char* name, const void* bits, const int64_t* shape, int ndim) {
+  REQUIRE(e && name && bits && shape, "null argument");
+  CK(cudaSetDevice(e->device));
+  auto it = e->dests.find(name);
+  if (it == e->dests.end()) {
+    if (!owned_name(e, name)) return 1;
+    set_err("tensor '%s' is not part of this model", name);
+    return XOTB200_ESTRICT;
+  }
+  Dest& d = it->second;
+  const bool ok = (ndim == 2 && shape[0] == d.rows && shape[1] == d.cols) || (ndim == 1 && d.rows == 1 && shape[0] == d.cols);
+  if (!ok) {
+    set_err("tensor '%s': shape [%lld%s%lld] does not fit the model's [%d, %d]", name, (long long)shape[0], ndim > 1 ? ", " : "", ndim > 1 ? (long long)shape[1] : 0LL,
+            d.rows, d.cols);
+    return XOTB200_ESTRICT;
+  }
+  return upload_tensor(e, d, bits);
+}
+
+int xotb200_lm_check_loaded(xotb200_lm* e) {
+  REQUIRE(e, "null engine");
+  for (auto& kv : e->dests)
+    if (!kv.second.loaded) {
+      set_err("tensor '%s' has not been loaded", kv.first.c_str());
+      return XOTB200_ESTRICT;
+    }
+  return 0;
+}
+
+int xotb200_lm_load_dir(xotb200_lm* e, const char* dir) {
+  REQUIRE(e && dir, "null argument");
+  CK(cudaSetDevice(e->device));
+  DIR* dp = opendir(dir);
+  if (!dp) { set_err("cannot open directory %s", dir); return XOTB200_EIO; }
+  std::vector<std::string> files;
+  while (dirent* de = readdir(dp)) {
+    const std::string n = de->d_name;
+    if (n.size() > 12 && n.substr(n.size() - 12) == ".safetensors") files.push_back(std::string(dir) + "/" + n);
+  }
+  closedir(dp);
+  std::sort(files.begin(), files.end());
+  if (files.empty()) { set_err("no *.safetensors in %s", dir); return XOTB200_EIO; }
+  for (auto& kv : e->dests) kv.second.loaded = false;
+  for (const std::string& path : files) {
+    const int fd = open(path.c_str(), O_RDONLY);
+    if (fd < 0) { set_err("cannot open %s", path.c_str()); return XOTB200_EIO; }
+    struct stat sb;
+    if (fstat(fd, &sb) != 0 || sb.st_size < 8) { close(fd); set_err("%s: too short", path.c_str()); return XOTB200_EIO; }
+    const char* base = static_cast<const char*>(mmap(nullptr, sb.st_size, PROT_READ, MAP_PRIVATE, fd, 0));
+    close(fd);
+    if (base == MAP_FAILED) { set_err("%s: mmap failed", path.c_str()); return XOTB200_EIO; }
+    int rc = 0;
+    uint64_t hlen = 0;
+    memcpy(&hlen, base, 8);
+    std::map<std::string, StEntry> hdr;
+    if (hlen > (uint64_t)sb.st_size - 8 || !parse_st_header(base + 8, hlen, hdr)) {
+      set_err("%s: bad safetensors header", path.c_str());
+      rc = XOTB200_EIO;
+    }
+    const char* data = base + 8 + hlen;
+    const int64_t data_len = sb.st_size - 8 - (int64_t)hlen;
+    for (auto it = hdr.begin(); rc == 0 && it != hdr.end(); ++it) {
+      const StEntry& en = it->second;
+      auto d = e->dests.find(it->first);
+      if (d == e->dests.end()) {
+        if (!owned_name(e, it->first)) continue;
+        set_err("%s: tensor '%s' is not part of this model", path.c_str(), it->first.c_str());
+        rc = XOTB200_ESTRICT;
+        break;
+      }
+      int64_t n = 1;
+      for (int64_t v : en.shape) n *= v;
+      if (en.dtype != "BF16") { set_err("tensor '%s': dtype %s, expected BF16", it->first.c_str(), en.dtype.c_str()); rc = XOTB200_ESTRICT; break; }
+      if (en.begin < 0 || en.end > data_len || en.end - en.begin != n * 2) { set_err("tensor '%s': inconsistent data_offsets", it->first.c_str()); rc = XOTB200_EIO; break; }
+      if (en.shape.empty() || en.shape.size() > 2) { set_err("tensor '%s': %zu dimensions", it->first.c_str(), en.shape.size()); rc = XOTB200_ESTRICT; break; }
+      rc = xotb200_lm_load_tensor(e, it->first.c_str(), data + en.begin, en.shape.data(), (int)en.shape.size());
+    }
+    munmap(const_cast<char*>(base), sb.st_size);
+    if (rc < 0) return rc;
+  }
+  return xotb200_lm_check_loaded(e);
+}
+
+int xotb200_lm_begin(xotb200_lm* e, int max_tokens, int max_requests, int page_size) {
+  REQUIRE(e, "null engine");
+  REQUIRE(max_tokens >= 1 && max_requests >= 1 && max_requests <= 4096, "max_tokens >= 1 and 1 <= max_requests <= 4096 required");
+  REQUIRE(page_size >= 0 && page_size <= 4096, "page_size out of range");
+  CK(cudaSetDevice(e->device));
+  CK(cudaStreamSynchronize(e->stream));
+  free_state(e);
+  const int P = page_size > 0 ? page_size : 64;
+  e->page_size = P;
+  e->max_requests = max_requests;
+  // every live request may hold one partly filled page: max_requests pages of slack
+  e->n_pages = cdiv(max_tokens, P) + max_requests;
+  e->pages_per_slot = cdiv(max_tokens, P) + 1;
+  for (auto& L : e->layers)
+    if (L.s.mixer == XOTB200_LM_MIX_LATENT_ATTN) {
+      const size_t bytes = (size_t)e->n_pages * P * (L.s.kv_rank + L.s.rot_dim) * e->esz;
+      CK(cudaMalloc(&L.pool, bytes));
+      CK(cudaMemsetAsync(L.pool, 0, bytes, e->stream));
+    }
+  const size_t tab = (size_t)max_requests * e->pages_per_slot;
+  CK(cudaHostAlloc(&e->h_table, tab * 4, cudaHostAllocDefault));
+  memset(e->h_table, 0, tab * 4);
+  CK(cudaMalloc(&e->d_table, tab * 4));
+  CK(cudaMemsetAsync(e->d_table, 0, tab * 4, e->stream));
+  if (e->state_floats) {
+    CK(cudaMalloc(&e->state, (size_t)max_requests * e->state_floats * 4));
+    CK(cudaMemsetAsync(e->state, 0, (size_t)max_requests * e->state_floats * 4, e->stream));
+  }
+  e->free_pages.clear();
+  for (int p = e->n_pages - 1; p >= 0; --p) e->free_pages.push_back(p);   // pages are handed out from the back: 0, 1, 2, ...
+  e->slot_len.assign(max_requests, 0);
+  e->slot_pages.assign(max_requests, 0);
+  CK(cudaStreamSynchronize(e->stream));
+  return 0;
+}
+
+int xotb200_lm_clear_request(xotb200_lm* e, int slot) {
+  REQUIRE(e && e->max_requests > 0, "no request state: call xotb200_lm_begin first");
+  REQUIRE(slot >= 0 && slot < e->max_requests, "slot %d out of range (%d)", slot, e->max_requests);
+  CK(cudaSetDevice(e->device));
+  for (int i = e->slot_pages[slot] - 1; i >= 0; --i) e->free_pages.push_back(e->h_table[(size_t)slot * e->pages_per_slot + i]);
+  e->slot_pages[slot] = 0;
+  e->slot_len[slot] = 0;
+  if (e->state_floats) {
+    CK(cudaMemsetAsync(e->state + (size_t)slot * e->state_floats, 0, e->state_floats * 4, e->stream));
+    CK(cudaStreamSynchronize(e->stream));
+  }
+  return 0;
+}
+
+int xotb200_lm_request_len(xotb200_lm* e, int slot, int* len) {
+  REQUIRE(e && len && slot >= 0 && slot < e->max_requests, "bad argument");
+  *len = e->slot_len[slot];
+  return 0;
+}
+
+int xotb200_lm_step(xotb200_lm* e, int n_seq, const int32_t* slots, const int32_t* counts, const int32_t* tokens, const float* hidden_f32,
+                    const int32_t* want_rows, int n_want, float* logits_f32, int32_t* argmax_i32, float* hidden_out_f32) {
+  REQUIRE(e && slots && counts && n_seq >= 1, "bad argument");
+  REQUIRE(e->max_requests > 0, "no request state: call xotb200_lm_begin first");
+  REQUIRE(e->first ? tokens != nullptr : hidden_f32 != nullptr, "the first shard takes token ids, every other shard the hidden state");
+  REQUIRE(e->last || hidden_out_f32, "a shard that is not the last returns the hidden state");
+  CK(cudaSetDevice(e->device));
+  TRY(xotb200_lm_check_loaded(e));
+  if (!e->last) n_want = 0;
+  const int D = e->cfg.width, V = e->cfg.vocab, P = e->page_size;
+  // ---- validate and plan on the host; nothing is changed before every check has passed
+  long M = 0;
+  int need_pages = 0;
+  std::vector<char> seen(e->max_requests, 0);
+  for (int i = 0; i < n_seq; ++i) {
+    REQUIRE(slots[i] >= 0 && slots[i] < e->max_requests, "slot %d out of range (%d)", slots[i], e->max_requests);
+    REQUIRE(!seen[slots[i]], "slot %d appears twice in one step", slots[i]);
+    seen[slots[i]] = 1;
+    REQUIRE(counts[i] >= 1, "request %d brings %d rows", i, counts[i]);
+    const int len = e->slot_len[slots[i]] + counts[i];
+    REQUIRE(cdiv(len, P) <= e->pages_per_slot, "slot %d would hold %d tokens, more than the cache was sized for", slots[i], len);
+    need_pages += cdiv(len, P) - e->slot_pages[slots[i]];
+    M += counts[i];
+  }
+  REQUIRE(M < (1L << 30), "too many rows");
+  REQUIRE(need_pages <= (int)e->free_pages.size(), "latent cache full: %d pages needed, %zu free (sized for fewer live tokens)", need_pages,
+          e->free_pages.size());
+  for (int w = 0; w < n_want; ++w) REQUIRE(want_rows && want_rows[w] >= 0 && want_rows[w] < M, "wanted row out of range");
+  if (e->first)
+    for (long m = 0; m < M; ++m) REQUIRE(tokens[m] >= 0 && tokens[m] < V, "token id %d outside the vocabulary of %d", tokens[m], V);
+  TRY(ensure_scratch(e, (int)M, n_want));
+  // distinct work-item sizes of the attention layers
+  std::vector<int> qpis;
+  for (auto& L : e->layers)
+    if (L.s.mixer == XOTB200_LM_MIX_LATENT_ATTN) {
+      const int q = std::max(1, 32 / L.s.heads);
+      if (std::find(qpis.begin(), qpis.end(), q) == qpis.end()) qpis.push_back(q);
+    }
+  size_t ints = 3 * (size_t)M + n_want + 4 * (size_t)n_seq;
+  for (int q : qpis)
+    for (int i = 0; i < n_seq; ++i) ints += 4 * (size_t)cdiv(counts[i], q);
+  if (ints > e->stage_cap) {
+    if (e->h_stage) cudaFreeHost(e->h_stage);
+    if (e->d_stage) cudaFree(e->d_stage);
+    e->h_stage = nullptr; e->d_stage = nullptr; e->stage_cap = 0;
+    const size_t cap = std::max<size_t>(ints * 2, 4096);
+    CK(cudaHostAlloc(&e->h_stage, cap * 4, cudaHostAllocDefault));
+    CK(cudaMalloc(&e->d_stage, cap * 4));
+    e->stage_cap = cap;
+  }
+  // ---- commit: pages, lengths, staging arrays
+  int* hs = e->h_stage;
+  int *h_tok = hs, *h_slot = hs + M, *h_pos = hs + 2 * M, *h_want = hs + 3 * M;
+  Item* h_seq = reinterpret_cast<Item*>(hs + 3 * M + n_want);
+  size_t off = 3 * (size_t)M + n_want + 4 * (size_t)n_seq;
+  StepPlan sp;
+  sp.M = (int)M;
+  sp.n_seq = n_seq;
+  int row = 0;
+  for (int i = 0; i < n_seq; ++i) {
+    const int sl = slots[i], len0 = e->slot_len[sl], len1 = len0 + counts[i];
+    const int np0 = e->slot_pages[sl], np1 = cdiv(len1, P);
+    for (int p = np0; p < np1; ++p) {
+      e->h_table[(size_t)sl * e->pages_per_slot + p] = e->free_pages.back();
+      e->free_pages.pop_back();
+    }
+    if (np1 > np0)
+      CK(cudaMemcpyAsync(e->d_table + (size_t)sl * e->pages_per_slot + np0, e->h_table + (size_t)sl * e->pages_per_slot + np0, (size_t)(np1 - np0) * 4,
+                         cudaMemcpyHostToDevice, e->stream));
+    e->slot_pages[sl] = np1;
+    e->slot_len[sl] = len1;
+    h_seq[i] = Item{row, counts[i], sl, len0};
+    for (int t = 0; t < counts[i]; ++t, ++row) {
+      h_tok[row] = e->first ? tokens[row] : 0;
+      h_slot[row] = sl;
+      h_pos[row] = len0 + t;
+    }
+  }
+  for (int w = 0; w < n_want; ++w) h_want[w] = want_rows[w];
+  std::map<int, std::pair<size_t, int>> item_off;
+  for (int q : qpis) {
+    Item* it = reinterpret_cast<Item*>(hs + off);
+    int n = 0;
+    for (int i = 0; i < n_seq; ++i)
+      for (int t = 0; t < counts[i]; t += q) it[n++] = Item{h_seq[i].row0 + t, std::min(q, counts[i] - t), h_seq[i].slot, h_seq[i].pos0 + t};
+    item_off[q] = {off, n};
+    off += 4 * (size_t)n;
+  }
+  CK(cudaEventRecord(e->ev0, e->stream));
+  CK(cudaMemcpyAsync(e->d_stage, hs, off * 4, cudaMemcpyHostToDevice, e->stream));
+  sp.tokens = e->d_stage;
+  sp.row_slot = e->d_stage + M;
+  sp.row_pos = e->d_stage + 2 * M;
+  sp.want = e->d_stage + 3 * M;
+  sp.seqs = reinterpret_cast<const Item*>(e->d_stage + 3 * M + n_want);
+  for (auto& kv : item_off) sp.items[kv.first] = {reinterpret_cast<const Item*>(e->d_stage + kv.second.first), kv.second.second};
+  if (!e->first) CK(cudaMemcpyAsync(e->x, hidden_f32, (size_t)M * D * 4, cudaMemcpyHostToDevice, e->stream));
+  {
+    int rc = e->esz == 2 ? run_layers<bf16>(e, sp, n_want) : run_layers<float>(e, sp, n_want);
+    if (rc < 0) { cudaStreamSynchronize(e->stream); return rc; }
+  }
+  // ---- results
+  if (e->last && n_want > 0) {
+    TRY(ensure_host_out(e, (size_t)n_want * V + n_want));
+    if (logits_f32) CK(cudaMemcpyAsync(e->h_out, e->logits, (size_t)n_want * V * 4, cudaMemcpyDeviceToHost, e->stream));
+    if (argmax_i32) CK(cudaMemcpyAsync(e->h_out + (size_t)n_want * V, e->d_argmax, (size_t)n_want * 4, cudaMemcpyDeviceToHost, e->stream));
+  } else if (!e->last) {
+    TRY(ensure_host_out(e, (size_t)M * D));
+    CK(cudaMemcpyAsync(e->h_out, e->x, (size_t)M * D * 4, cudaMemcpyDeviceToHost, e->stream));
+  }
+  CK(cudaEventRecord(e->ev1, e->stream));
+  CK(cudaStreamSynchronize(e->stream));
+  CK(cudaEventElapsedTime(&e->last_ms, e->ev0, e->ev1));
+  if (e->last && n_want > 0) {
+    if (logits_f32) memcpy(logits_f32, e->h_out, (size_t)n_want * V * 4);
+    if (argmax_i32) memcpy(argmax_i32, e->h_out + (size_t)n_want * V, (size_t)n_want * 4);
+  } else if (!e->last) {
+    memcpy(hidden_out_f32, e->h_out, (size_t)M * D * 4);
+  }
+  return 0;
+}
+
+int xotb200_lm_set_trace(xotb200_lm* e, int on) {
+  REQUIRE(e, "null engine");
+  e->trace = on != 0;
+  e->trace_floats = 0;
+  return 0;
+}
+
+int xotb200_lm_read_trace(xotb200_lm* e, float* out, int64_t n_floats) {
+  REQUIRE(e && out, "null argument");
+  REQUIRE(e->trace && e->trace_floats > 0, "no trace recorded: enable it before the step");
+  REQUIRE((size_t)n_floats == e->trace_floats, "trace holds %zu floats, caller asked for %lld", e->trace_floats, (long long)n_floats);
+  CK(cudaSetDevice(e->device));
+  CK(cudaMemcpyAsync(out, e->trace_buf, e->trace_floats * 4, cudaMemcpyDeviceToHost, e->stream));
+  CK(cudaStreamSynchronize(e->stream));
+  return 0;
+}
+
+int xotb200_lm_set_gemm_mode(xotb200_lm* e, int mode) {
+  REQUIRE(e && mode >= 0 && mode <= 1, "gemm mode must be 0 or 1");
+  e->gemm_mode = mode;
+  return 0;
+}
+
+int xotb200_lm_kernel_launches(xotb200_lm* e, int64_t* count) {
+  REQUIRE(e && count, "null argument");
+  *count = e->launches;
+  return 0;
+}
+
+int xotb200_lm_weight_bytes(xotb200_lm* e, int64_t* bytes) {
+  REQUIRE(e && bytes, "null argument");
+  *bytes = (int64_t)(e->blob_elems * e->esz);
+  return 0;
+}
+
+int xotb200_lm_cache_stats(xotb200_lm* e, int* pages_total, int* pages_free, int* page_size) {
+  REQUIRE(e, "null engine");
+  if (pages_total) *pages_total = e->n_pages;
+  if (pages_free) *pages_free = (int)e->free_pages.size();
+  if (page_size) *page_size = e->page_size;
+  return 0;
+}
+
+int xotb200_lm_last_step_ms(xotb200_lm* e, float* ms) {
+  REQUIRE(e && ms, "null argument");
+  *ms = e->last_ms;
+  return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,527 @@
+// layered_kernels.cuh — device code of the layered-model engine (libxotb200_lm.so): decoder models given as a LIST of layers,
+// each a token mixer (latent attention over a paged latent cache, or a generalised delta-rule recurrence over a per-request
+// state) and an optional feed-forward, with grouped RMS norms before and after every sublayer.
+//
+// Number formats: every kernel is a template over T, the storage type of weights, GEMM inputs and the latent cache
+// (__nv_bfloat16 when serving, float for the all-32-bit mode).  Whatever T is, these are fp32: the residual stream, every norm,
+// positions / angles / rotations, attention scores and softmax, gates, decays, unit keys, the recurrent state, GEMM accumulators.
+//
+// A step works on a PACKED batch: M token rows of several requests back to back (no padding); row_slot[m] / row_pos[m] say which
+// request a row belongs to and where it stands in it.  The same kernels serve prompts (many rows per request) and decoding (one
+// row per request); the small-M projection kernel (gemv_rows_kernel) is the decode specialisation.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace xl {
+
+typedef __nv_bfloat16 bf16;
+
+template <typename T> __device__ __forceinline__ float ldf(const T* p);
+template <> __device__ __forceinline__ float ldf<float>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float ldf<bf16>(const bf16* p) { return __bfloat162float(*p); }
+template <typename T> __device__ __forceinline__ void stf(T* p, float v);
+template <> __device__ __forceinline__ void stf<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void stf<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf(-z)); }
+
+// Where a request's token lives in a paged pool: page_table[slot * pages_per_slot + pos / P] * P + pos % P.
+struct Paging {
+  const int* page_table;
+  int pages_per_slot;
+  int page_size;
+  __device__ __forceinline__ size_t row(int slot, int pos) const {
+    return (size_t)page_table[(size_t)slot * pages_per_slot + pos / page_size] * page_size + pos % page_size;
+  }
+};
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// embedding:  x[m, :] = embed[token[m], :]   (fp32 residual)
+// ---------------------------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void embed_rows_kernel(const T* __restrict__ embed, const int* __restrict__ tokens, float* __restrict__ x, int D) {
+  const int m = blockIdx.x;
+  const T* src = embed + (size_t)tokens[m] * D;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) x[(size_t)m * D + d] = ldf(src + d);
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// Fused "close one sublayer, open the next":   x += groupnorm(y) * w_post ;  h = groupnorm(x) * w_pre
+// groupnorm: the row is cut into G equal consecutive parts, each divided by sqrt(mean(part^2) + eps).  One warp per part, so both
+// norms and the residual sum need no block-wide exchange.  y / w_post may be NULL (first sublayer), h / w_pre may be NULL (no
+// sublayer follows).  src_rows (may be NULL) gathers: output row m reads x row src_rows[m] and does not write x (used for the
+// final norm on the rows whose logits are wanted).
+// ---------------------------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void residual_groupnorm_kernel(float* __restrict__ x, const float* __restrict__ y, const T* __restrict__ w_post,
+                                          const T* __restrict__ w_pre, T* __restrict__ h, const int* __restrict__ src_rows, int D, int G,
+                                          float eps) {
+  const int m = blockIdx.x;
+  const int xm = src_rows ? src_rows[m] : m;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const int Dg = D / G;
+  for (int g = warp; g < G; g += nw) {
+    float* xr = x + (size_t)xm * D + (size_t)g * Dg;
+    float ry = 0.f;
+    if (y) {
+      const float* yr = y + (size_t)m * D + (size_t)g * Dg;
+      float s = 0.f;
+      for (int d = lane; d < Dg; d += 32) { const float v = yr[d]; s = fmaf(v, v, s); }
+      ry = 1.0f / sqrtf(warp_sum(s) / (float)Dg + eps);
+    }
+    float s2 = 0.f;
+    for (int d = lane; d < Dg; d += 32) {
+      float v = xr[d];
+      if (y) {
+        v += y[(size_t)m * D + (size_t)g * Dg + d] * ry * ldf(w_post + (size_t)g * Dg + d);
+        xr[d] = v;
+      }
+      s2 = fmaf(v, v, s2);
+    }
+    if (h) {
+      const float rx = 1.0f / sqrtf(warp_sum(s2) / (float)Dg + eps);
+      for (int d = lane; d < Dg; d += 32) stf(h + (size_t)m * D + (size_t)g * Dg + d, xr[d] * rx * ldf(w_pre + (size_t)g * Dg + d));
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// Plain RMS norm of n columns of an fp32 matrix (a projection's output) into a T matrix:  out[m, :] = in[m, col0:col0+n] / rms * w
+// One warp per row.
+// ---------------------------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void rmsnorm_cols_kernel(const float* __restrict__ in, int ld_in, int col0, int n, const T* __restrict__ w, T* __restrict__ out,
+                                    int ld_out, int M, float eps) {
+  const int m = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (m >= M) return;
+  const float* r = in + (size_t)m * ld_in + col0;
+  float s = 0.f;
+  for (int d = lane; d < n; d += 32) s = fmaf(r[d], r[d], s);
+  const float rs = 1.0f / sqrtf(warp_sum(s) / (float)n + eps);
+  for (int d = lane; d < n; d += 32) stf(out + (size_t)m * ld_out + d, r[d] * rs * ldf(w + d));
+}
+
+// Rotation of one pair by the angle pos * freq (fp32 throughout).  layout 0: pairs (2i, 2i+1); 1: pairs (i, i + dims/2).
+__device__ __forceinline__ void rot_pair_index(int i, int dims, int layout, int& a, int& b) {
+  if (layout == 0) { a = 2 * i; b = 2 * i + 1; }
+  else { a = i; b = i + dims / 2; }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// Latent cache append.  proj[m, col0 : col0 + R + dr] is the down-projection of row m: the first R columns are RMS-normed (weight
+// w_norm) into the latent, the last dr are the shared key part, of which the first rot_dims entries are rotated by the row's
+// position.  Both go to the row's place in the paged pool: pool[(page * P + offset) * (R + dr) + ...].  One warp per row.
+// ---------------------------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void latent_append_kernel(const float* __restrict__ proj, int ld, int col0, int R, int dr, const T* __restrict__ w_norm, float eps,
+                                     const float* __restrict__ freqs, int rot_dims, int layout, const int* __restrict__ row_slot,
+                                     const int* __restrict__ row_pos, Paging pg, T* __restrict__ pool, int M) {
+  const int m = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (m >= M) return;
+  const float* r = proj + (size_t)m * ld + col0;
+  T* dst = pool + pg.row(row_slot[m], row_pos[m]) * (size_t)(R + dr);
+  float s = 0.f;
+  for (int d = lane; d < R; d += 32) s = fmaf(r[d], r[d], s);
+  const float rs = 1.0f / sqrtf(warp_sum(s) / (float)R + eps);
+  for (int d = lane; d < R; d += 32) stf(dst + d, r[d] * rs * ldf(w_norm + d));
+  const float p = (float)row_pos[m];
+  const float* kr = r + R;
+  for (int i = lane; i < rot_dims / 2; i += 32) {
+    int a, b;
+    rot_pair_index(i, rot_dims, layout, a, b);
+    const float ang = p * freqs[i], c = cosf(ang), sn = sinf(ang);
+    const float u = kr[a], v = kr[b];
+    stf(dst + R + a, u * c - v * sn);
+    stf(dst + R + b, v * c + u * sn);
+  }
+  for (int d = rot_dims + lane; d < dr; d += 32) stf(dst + R + d, kr[d]);
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// Query split.  qraw[m, h * (dn + dr) + ...] (fp32 projection output, leading dimension ld, first column col0) is cut per head
+// into the unrotated part -> qn[m, h, dn] (T: the operand of the key-absorption product) and the rotated part, turned by the
+// row's position -> qfull[m, h, R : R + dr] (fp32; columns [0, R) are filled by the absorption product).  One warp per (row, head).
+// ---------------------------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void query_split_kernel(const float* __restrict__ qraw, int ld, int col0, int H, int dn, int dr, int R, const float* __restrict__ freqs,
+                                   int rot_dims, int layout, const int* __restrict__ row_pos, T* __restrict__ qn, float* __restrict__ qfull,
+                                   int M) {
+  const int idx = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (idx >= M * H) return;
+  const int m = idx / H, h = idx % H;
+  const float* q = qraw + (size_t)m * ld + col0 + (size_t)h * (dn + dr);
+  for (int d = lane; d < dn; d += 32) stf(qn + ((size_t)m * H + h) * dn + d, q[d]);
+  float* out = qfull + ((size_t)m * H + h) * (R + dr) + R;
+  const float p = (float)row_pos[m];
+  const float* qr = q + dn;
+  for (int i = lane; i < rot_dims / 2; i += 32) {
+    int a, b;
+    rot_pair_index(i, rot_dims, layout, a, b);
+    const float ang = p * freqs[i], c = cosf(ang), sn = sinf(ang);
+    const float u = qr[a], v = qr[b];
+    out[a] = u * c - v * sn;
+    out[b] = v * c + u * sn;
+  }
+  for (int d = rot_dims + lane; d < dr; d += 32) out[d] = qr[d];
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// Latent attention over the paged pool, in the ABSORBED form: with q~ = W_uk[h]^T q_unrotated (R numbers per head, computed by a
+// batched product before this kernel) the score of query (m, h) against cached token j is (q~ . c_j + q_rot . kr_j) * scale, and
+// the head's output is W_uv[h] (sum_j p_j c_j) — so every head reads the SAME cached rows [c_j | kr_j] and nothing per head is
+// ever expanded or stored.  Key range of a query at position i: max(0, i - window + 1) .. i (window == 0: 0 .. i).
+//
+// One CTA serves one work item = up to `q_per_item` consecutive rows of one request, all H heads; one WARP owns one (row, head)
+// pair: lane j scores key j of a 32-key tile held in shared memory (fp32, row stride padded odd), the softmax statistics are
+// exchanged by shuffles, and the lanes then split the R latent columns of the running sum sum_j p_j c_j between them
+// (NACC = ceil(R / 32) registers).  Output: olat[m, h, R] (T), times sigmoid(gate[m, h]) when the mixer has an output gate.
+// ---------------------------------------------------------------------------------------------------------------------------
+struct Item {
+  int row0;     // first packed row
+  int n_rows;   // rows of this item (consecutive positions of one request)
+  int slot;     // request
+  int pos0;     // position of row0
+};
+
+template <typename T, int NACC>
+__global__ void latent_attention_kernel(const float* __restrict__ qfull, const T* __restrict__ pool, Paging pg, const Item* __restrict__ items,
+                                        int H, int R, int dr, float scale, int window, const float* __restrict__ gate, int gate_ld,
+                                        int gate_col0, T* __restrict__ olat) {
+  extern __shared__ float smem[];
+  const Item it = items[blockIdx.x];
+  const int W = R + dr, WS = W | 1;                 // odd row stride: lane j reading row j is conflict-free
+  float* ktile = smem;                              // [32][WS]
+  float* qs = smem + 32 * WS;                       // [warps][W]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const int pair = blockIdx.y * nw + warp;         // (row, head) pair of this warp
+  const bool active = pair < it.n_rows * H;
+  const int qi = active ? pair / H : 0, h = active ? pair % H : 0;
+  const int m = it.row0 + qi, pos = it.pos0 + qi;
+  float* q = qs + (size_t)warp * W;
+  if (active) {
+    const float* src = qfull + ((size_t)m * H + h) * W;
+    for (int d = lane; d < W; d += 32) q[d] = src[d];
+  }
+  const int last = it.pos0 + it.n_rows - 1;
+  const int first = window > 0 ? max(0, it.pos0 - window + 1) : 0;
+  float acc[NACC];
+#pragma unroll
+  for (int a = 0; a < NACC; ++a) acc[a] = 0.f;
+  float mx = -INFINITY, den = 0.f;
+  for (int j0 = first; j0 <= last; j0 += 32) {
+    __syncthreads();
+    // stage 32 cached rows (fp32) — rows past `last` are zero-filled
+    for (int e = threadIdx.x; e < 32 * W; e += blockDim.x) {
+      const int jr = e / W, d = e % W, j = j0 + jr;
+      ktile[jr * WS + d] = j <= last ? ldf(pool + pg.row(it.slot, j) * (size_t)W + d) : 0.f;
+    }
+    __syncthreads();
+    if (!active) continue;
+    const int j = j0 + lane;
+    const bool vis = j <= pos && (window == 0 || pos - j < window);
+    float s = 0.f;
+    const float* kr = ktile + lane * WS;
+    for (int d = 0; d < W; ++d) s = fmaf(q[d], kr[d], s);
+    s = vis ? s * scale : -INFINITY;
+    const float tmax = warp_max(s);
+    if (tmax == -INFINITY) continue;                // no visible key in this tile (warp-uniform)
+    const float nmx = fmaxf(mx, tmax);
+    const float corr = expf(mx - nmx);              // mx == -inf: exp(-inf) = 0
+    const float p = vis ? expf(s - nmx) : 0.f;
+    den = den * corr + warp_sum(p);
+    mx = nmx;
+#pragma unroll
+    for (int a = 0; a < NACC; ++a) acc[a] *= corr;
+    for (int jr = 0; jr < 32; ++jr) {
+      const float pj = __shfl_sync(0xffffffffu, p, jr);
+      if (pj == 0.f) continue;                      // warp-uniform
+      const float* c = ktile + jr * WS;
+#pragma unroll
+      for (int a = 0; a < NACC; ++a) {
+        const int d = a * 32 + lane;
+        if (d < R) acc[a] = fmaf(pj, c[d], acc[a]);
+      }
+    }
+  }
+  if (!active) return;
+  float g = 1.0f / den;
+  if (gate) g *= sigmoidf_(gate[(size_t)m * gate_ld + gate_col0 + h]);
+  T* out = olat + ((size_t)m * H + h) * R;
+#pragma unroll
+  for (int a = 0; a < NACC; ++a) {
+    const int d = a * 32 + lane;
+    if (d < R) stf(out + d, acc[a] * g);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// Generalised delta rule.  Per head, with key size dk and value size dv, the state S [dk, dv] (fp32, one per request and layer)
+// moves per token as   S <- diag(w) S - (a * u)(u^T S) + k v^T   (both products read the old S),   o = S^T r,
+// where u = k / sqrt(|k|^2 + 1e-6), w = exp(-exp(-1/2) * sigmoid(decay logit + bias)) and a = sigmoid(removal logit + bias).
+// The COLUMNS of S (value index) never mix, so a column lives in the registers of `P` cooperating lanes (KPT key rows each,
+// row i = e * P + part) and the only exchange per token is a P-lane shuffle reduction of u^T S and of S^T r.
+// One CTA = one (request, head, group of value columns); tokens of the step are staged CH at a time in shared memory, where
+// w, a * u, u are computed once per token for all columns.
+//   proj: fp32 [M, ld] projection output with the r / k / v / a blocks (H * d columns each) at the given column offsets;
+//   wlog: fp32 [M, H * dk] decay logits (low-rank branch output), to which w_bias is added;   o_raw: fp32 [M, H * dv].
+// ---------------------------------------------------------------------------------------------------------------------------
+template <typename T, int KPT, int P>
+__global__ void delta_rule_kernel(const float* __restrict__ proj, int ld, int col_r, int col_k, int col_v, int col_a, const float* __restrict__ wlog,
+                                  const T* __restrict__ w_bias, const T* __restrict__ a_bias, const Item* __restrict__ seqs, int H, int dk,
+                                  int dv, float* __restrict__ state, size_t state_slot_stride, float* __restrict__ o_raw) {
+  constexpr int CH = 8;
+  constexpr int DKP = KPT * P;                       // padded key size
+  __shared__ float s_w[CH][DKP], s_au[CH][DKP], s_u[CH][DKP], s_k[CH][DKP], s_r[CH][DKP];
+  extern __shared__ float s_v[];                     // [CH][dv]
+  const Item sq = seqs[blockIdx.x / H];
+  const int h = blockIdx.x % H;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr int CPW = 32 / P;                        // columns per warp
+  const int col = (blockIdx.y * (blockDim.x >> 5) + warp) * CPW + lane / P, part = lane % P;   // grid.y splits the value columns
+  const bool col_ok = col < dv;
+  float* S = state + (size_t)sq.slot * state_slot_stride + (size_t)h * dk * dv;
+  float s[KPT];
+#pragma unroll
+  for (int e = 0; e < KPT; ++e) {
+    const int i = e * P + part;
+    s[e] = (col_ok && i < dk) ? S[(size_t)i * dv + col] : 0.f;
+  }
+  for (int t0 = 0; t0 < sq.n_rows; t0 += CH) {
+    const int nt = min(CH, sq.n_rows - t0);
+    __syncthreads();
+    // stage: one warp per token computes the head's vectors
+    for (int t = warp; t < nt; t += (blockDim.x >> 5)) {
+      const size_t m = (size_t)sq.row0 + t0 + t;
+      const float* pr = proj + m * ld;
+      float ss = 0.f;
+      for (int i = lane; i < dk; i += 32) { const float kv = pr[col_k + h * dk + i]; ss = fmaf(kv, kv, ss); }
+      const float inv = 1.0f / sqrtf(warp_sum(ss) + 1e-6f);
+      for (int i = lane; i < DKP; i += 32) {
+        float w = 0.f, au = 0.f, u = 0.f, kk = 0.f, rr = 0.f;
+        if (i < dk) {
+          kk = pr[col_k + h * dk + i];
+          rr = pr[col_r + h * dk + i];
+          u = kk * inv;
+          au = sigmoidf_(pr[col_a + h * dk + i] + ldf(a_bias + h * dk + i)) * u;
+          w = expf(-0.60653065971263342f * sigmoidf_(wlog[m * (size_t)(H * dk) + h * dk + i] + ldf(w_bias + h * dk + i)));
+        }
+        s_w[t][i] = w; s_au[t][i] = au; s_u[t][i] = u; s_k[t][i] = kk; s_r[t][i] = rr;
+      }
+      for (int j = lane; j < dv; j += 32) s_v[t * dv + j] = pr[col_v + h * dv + j];
+    }
+    __syncthreads();
+    for (int t = 0; t < nt; ++t) {
+      float dot = 0.f;
+#pragma unroll
+      for (int e = 0; e < KPT; ++e) dot = fmaf(s_u[t][e * P + part], s[e], dot);
+#pragma unroll
+      for (int o = P / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+      const float vj = col_ok ? s_v[t * dv + col] : 0.f;
+      float out = 0.f;
+#pragma unroll
+      for (int e = 0; e < KPT; ++e) {
+        const int i = e * P + part;
+        s[e] = fmaf(s_w[t][i], s[e], fmaf(-s_au[t][i], dot, s_k[t][i] * vj));
+        out = fmaf(s[e], s_r[t][i], out);
+      }
+#pragma unroll
+      for (int o = P / 2; o > 0; o >>= 1) out += __shfl_xor_sync(0xffffffffu, out, o);
+      if (col_ok && part == 0) o_raw[((size_t)sq.row0 + t0 + t) * (size_t)(H * dv) + h * dv + col] = out;
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < KPT; ++e) {
+    const int i = e * P + part;
+    if (col_ok && i < dk) S[(size_t)i * dv + col] = s[e];
+  }
+}
+
+// Output side of the delta-rule mixer: per (row, head) o / rms(o) * w_norm * sigmoid(gate) -> T, the operand of the output product.
+template <typename T>
+__global__ void head_norm_gate_kernel(const float* __restrict__ o_raw, const T* __restrict__ w_norm, const float* __restrict__ gate, int gate_ld,
+                                      int gate_col0, T* __restrict__ out, int H, int dv, float eps, int M) {
+  const int idx = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (idx >= M * H) return;
+  const int m = idx / H, h = idx % H;
+  const float* o = o_raw + (size_t)m * H * dv + (size_t)h * dv;
+  float s = 0.f;
+  for (int d = lane; d < dv; d += 32) s = fmaf(o[d], o[d], s);
+  const float rs = 1.0f / sqrtf(warp_sum(s) / (float)dv + eps);
+  for (int d = lane; d < dv; d += 32)
+    stf(out + (size_t)m * H * dv + (size_t)h * dv + d,
+        o[d] * rs * ldf(w_norm + h * dv + d) * sigmoidf_(gate[(size_t)m * gate_ld + gate_col0 + h * dv + d]));
+}
+
+// out[m, :n] = tanh(in[m, col0 : col0 + n])  (fp32 in, T out): the low-rank decay branch between its two products
+template <typename T>
+__global__ void tanh_cols_kernel(const float* __restrict__ in, int ld, int col0, int n, T* __restrict__ out, int M) {
+  const size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+  if (i >= (size_t)M * n) return;
+  const size_t m = i / n, d = i % n;
+  stf(out + i, tanhf(in[m * ld + col0 + d]));
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// Products.  C[z][m, n] = sum_k A[z][m, k] * B[z][n, k]   with fp32 accumulation; A row-major (lda), B addressed by two strides
+// (sbn, sbk) so that a weight stored [K, N] is used without a transposed copy, z = batch (per-head products) via element offsets.
+// EPI 1: C = relu(C)^2.
+// gemm_tiled_kernel: 64 x 64 x 16 shared-memory tiles, 256 threads, 4 x 4 outputs per thread, fp32 FMA (exact fp32 in the 32-bit mode).
+// ---------------------------------------------------------------------------------------------------------------------------
+template <typename TA, typename TB, typename TC, int EPI>
+__global__ void __launch_bounds__(256)
+gemm_tiled_kernel(const TA* __restrict__ A, long lda, long a_batch, const TB* __restrict__ B, long sbn, long sbk, long b_batch, TC* __restrict__ C,
+                  long ldc, long c_batch, int M, int N, int K) {
+  constexpr int BM = 64, BN = 64, BK = 16;
+  __shared__ float As[BK][BM + 4], Bs[BK][BN + 4];
+  A += (size_t)blockIdx.z * a_batch;
+  B += (size_t)blockIdx.z * b_batch;
+  C += (size_t)blockIdx.z * c_batch;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+  float acc[4][4] = {};
+  for (int k0 = 0; k0 < K; k0 += BK) {
+    for (int e = threadIdx.x; e < BM * BK; e += 256) {
+      const int r = e / BK, k = e % BK;
+      As[k][r] = (m0 + r < M && k0 + k < K) ? ldf(A + (size_t)(m0 + r) * lda + k0 + k) : 0.f;
+    }
+    if (sbk == 1) {
+      for (int e = threadIdx.x; e < BN * BK; e += 256) {
+        const int r = e / BK, k = e % BK;
+        Bs[k][r] = (n0 + r < N && k0 + k < K) ? ldf(B + (size_t)(n0 + r) * sbn + k0 + k) : 0.f;
+      }
+    } else {
+      for (int e = threadIdx.x; e < BN * BK; e += 256) {
+        const int k = e / BN, r = e % BN;
+        Bs[k][r] = (n0 + r < N && k0 + k < K) ? ldf(B + (size_t)(n0 + r) * sbn + (size_t)(k0 + k) * sbk) : 0.f;
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < BK; ++k) {
+      float a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = As[k][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) b[j] = Bs[k][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int m = m0 + ty * 4 + i, n = n0 + tx * 4 + j;
+      if (m < M && n < N) {
+        float v = acc[i][j];
+        if (EPI == 1) { v = fmaxf(v, 0.f); v *= v; }
+        stf(C + (size_t)m * ldc + n, v);
+      }
+    }
+}
+
+// gemv_rows_kernel: the decode form (M <= MR rows, B contiguous along k).  One warp per output column n: the weight row is read
+// ONCE, 16 bytes per lane per step, and multiplied into all M activation rows (held in shared memory as fp32).
+template <typename TA, typename TB, typename TC, int EPI, int MR>
+__global__ void __launch_bounds__(256)
+gemv_rows_kernel(const TA* __restrict__ A, long lda, long a_batch, const TB* __restrict__ B, long sbn, long b_batch, TC* __restrict__ C, long ldc,
+                 long c_batch, int M, int N, int K) {
+  extern __shared__ float a_s[];                     // [M][K]
+  A += (size_t)blockIdx.z * a_batch;
+  B += (size_t)blockIdx.z * b_batch;
+  C += (size_t)blockIdx.z * c_batch;
+  for (int e = threadIdx.x; e < M * K; e += blockDim.x) a_s[e] = ldf(A + (size_t)(e / K) * lda + e % K);
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  constexpr int VEC = 16 / sizeof(TB);
+  for (int n = blockIdx.x * nw + warp; n < N; n += gridDim.x * nw) {
+    const TB* b = B + (size_t)n * sbn;
+    float acc[MR];
+#pragma unroll
+    for (int m = 0; m < MR; ++m) acc[m] = 0.f;
+    const bool vec_ok = (K % VEC == 0) && ((reinterpret_cast<uintptr_t>(b) & 15) == 0);
+    if (vec_ok) {
+      for (int k = lane * VEC; k < K; k += 32 * VEC) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(b + k);
+        const TB* bv = reinterpret_cast<const TB*>(&raw);
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) {
+          const float w = ldf(bv + v);
+#pragma unroll
+          for (int m = 0; m < MR; ++m)
+            if (m < M) acc[m] = fmaf(a_s[m * K + k + v], w, acc[m]);
+        }
+      }
+    } else {
+      for (int k = lane; k < K; k += 32) {
+        const float w = ldf(b + k);
+#pragma unroll
+        for (int m = 0; m < MR; ++m)
+          if (m < M) acc[m] = fmaf(a_s[m * K + k], w, acc[m]);
+      }
+    }
+#pragma unroll
+    for (int m = 0; m < MR; ++m) {
+      float v = warp_sum(acc[m]);
+      if (m < M && lane == 0) {
+        if (EPI == 1) { v = fmaxf(v, 0.f); v *= v; }
+        stf(C + (size_t)m * ldc + n, v);
+      }
+    }
+  }
+}
+
+// lowest-index argmax of every row of an fp32 matrix (greedy sampling on the device)
+__global__ void argmax_rows_kernel(const float* __restrict__ logits, int V, int* __restrict__ out) {
+  __shared__ float bv[32];
+  __shared__ int bi[32];
+  const float* r = logits + (size_t)blockIdx.x * V;
+  float best = -INFINITY;
+  int idx = 0x7fffffff;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float v = r[i];
+    if (v > best || (v == best && i < idx)) { best = v; idx = i; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+    if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
+  }
+  if ((threadIdx.x & 31) == 0) { bv[threadIdx.x >> 5] = best; bi[threadIdx.x >> 5] = idx; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
+      if (bv[w] > best || (bv[w] == best && bi[w] < idx)) { best = bv[w]; idx = bi[w]; }
+    out[blockIdx.x] = idx;
+  }
+}
+
+// weights arrive as bf16 bit patterns: widen (or copy) rows into their place in the T-typed blob
+template <typename T>
+__global__ void store_rows_kernel(const bf16* __restrict__ src, T* __restrict__ dst, size_t n) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    stf(dst + i, __bfloat162float(src[i]));
+}
+__global__ void copy_rows_f32_kernel(const float* __restrict__ src, float* __restrict__ dst, int ld_src, int ld_dst, int n, int M) {
+  const size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+  if (i >= (size_t)M * n) return;
+  dst[(i / n) * ld_dst + i % n] = src[(i / n) * ld_src + i % n];
+}
+
+}  // namespace xl
