@@ -180,6 +180,145 @@ class ContinuousRing:
     return {k: v.ids for k, v in self.finished.items()}
 
 
+class ContinuousBatch:
+  """Continuous batching for the layered engine (`LayeredShard`, libxotb200_lm.so).  Where `ContinuousRing` interleaves batch-1
+  streams over persistent kernels, this engine takes a PACKED batch per step: for every participating request its next rows — a
+  portion of its prompt or its one decoded token — against a paged cache and per-slot recurrent state.  So one scheduling round is
+
+    admit    waiting requests take a slot (`RequestSlots`) while slots are free and the page pool can hold prompt + max_tokens;
+    pack     every decoding request brings 1 row; prompts still being read bring their next portion, up to `token_budget` rows a
+             step in all (a long prompt is read in portions and never stalls the decoders for more than one budget);
+    step     one `LayeredShard.step` (several shards: the fp32 residual stream is handed from one to the next);
+    sample   greedy ids come from the device arg-max; with a temperature the logits go through the engine's sampler
+             (`reference_sample`: temperature, top-k, seeded noise);
+    emit     `on_token(request_id, [id], finished)` once per token as the reference's Node does (node.py:119-147); finished
+             requests give their slot, pages and state back.
+
+  `engines`: LayeredShard objects covering the model in order (usually one)."""
+
+  def __init__(self, engines, max_requests: int, max_tokens: int, page_size: int = 0, token_budget: int = 2048,
+               on_token: Optional[TokenCallback] = None, temp: float = 0.0, top_k: Optional[int] = 35, seed: int = 1234):
+    from .layered import DEFAULT_PAGE, RequestSlots
+    self.engines = list(engines) if isinstance(engines, (list, tuple)) else [engines]
+    assert self.engines[0].is_first and self.engines[-1].is_last, "engines must cover the model in order"
+    assert max_requests >= 1 and token_budget >= 1
+    self.page = int(page_size) or DEFAULT_PAGE
+    self.max_tokens, self.budget = int(max_tokens), int(token_budget)
+    for e in self.engines:
+      e.begin_pool(self.max_tokens, int(max_requests), self.page)
+    self.tables = [RequestSlots(e) for e in self.engines]
+    self.on_token, self.temp, self.top_k = on_token, float(temp), top_k
+    self._rng = np.random.default_rng(seed)
+    self.waiting: Deque[_Req] = deque()
+    self.active: List[_Req] = []
+    self.finished: Dict[str, _Req] = {}
+    self.reserved_pages = 0                          # pages promised to admitted requests (prompt + max_tokens each)
+    self._lock = threading.Lock()
+    self.stats = {"steps": 0, "rows": 0, "tokens": 0, "prefill_portions": 0}
+
+  def _pages(self, n_tokens: int) -> int:
+    return (n_tokens + self.page - 1) // self.page
+
+  def submit(self, request_id: str, prompt_ids, max_tokens: int, eos_token_id: Optional[int] = None) -> None:
+    p = np.asarray(prompt_ids, dtype=np.int32).reshape(1, -1)
+    if p.shape[1] < 1 or max_tokens < 1:
+      raise ValueError("a request needs at least one prompt token and one token to generate")
+    if p.shape[1] + max_tokens > self.max_tokens:
+      raise ValueError(f"request {request_id!r}: {p.shape[1]} prompt + {max_tokens} generated tokens exceed the cache of {self.max_tokens} tokens")
+    with self._lock:
+      self.waiting.append(_Req(request_id, p, int(max_tokens), eos_token_id))
+
+  def pending(self) -> bool:
+    with self._lock:
+      return bool(self.waiting) or bool(self.active)
+
+  def _admit(self) -> None:
+    total_pages = self.engines[0].cache_stats()["pages_total"]
+    while self.tables[0].free:
+      with self._lock:
+        if not self.waiting:
+          return
+        r = self.waiting[0]
+        need = self._pages(r.prompt.shape[1] + r.max_tokens)
+        if self.reserved_pages + need > total_pages:
+          return                                     # the head of the queue waits for pages; no overtaking
+        self.waiting.popleft()
+      self.reserved_pages += need
+      for t in self.tables:
+        r.slot = t.acquire(r.request_id)
+      r.pos = 0
+      self.active.append(r)
+
+  def _emit(self, r: _Req, tok: int) -> None:
+    r.ids.append(tok)
+    r.n_out += 1
+    self.stats["tokens"] += 1
+    r.done = r.n_out >= r.max_tokens or (r.eos_token_id is not None and tok == r.eos_token_id)
+    if self.on_token is not None:
+      self.on_token(r.request_id, [tok], r.done)
+
+  def _sample(self, logits: np.ndarray) -> np.ndarray:
+    from .inference.b200_engine import reference_sample
+    q = self._rng.exponential(1.0, size=logits.shape).astype(np.float32)
+    return reference_sample(logits, self.temp, self.top_k, q).reshape(-1)
+
+  def step(self) -> bool:
+    """one scheduling round; False when nothing is left to do"""
+    self._admit()
+    if not self.active:
+      return False
+    left = self.budget
+    batch, rows = [], []
+    for r in self.active:                            # decoders first: one row each
+      if r.pos >= r.prompt.shape[1]:
+        batch.append(r)
+        rows.append(np.array([r.last_token], dtype=np.int32))
+        left -= 1
+    for r in self.active:                            # then prompt portions, oldest first
+      n_prompt = r.prompt.shape[1]
+      if r.pos < n_prompt and left > 0:
+        n = min(left, n_prompt - r.pos)
+        batch.append(r)
+        rows.append(r.prompt[0, r.pos:r.pos + n])
+        left -= n
+        self.stats["prefill_portions"] += 1
+    counts = [len(x) for x in rows]
+    data = rows
+    greedy = self.temp <= 0.0
+    for e in self.engines:
+      slots = [r.slot for r in batch]
+      if e.is_last:
+        logits, ids = e.step(slots, data, logits=not greedy, argmax=greedy)
+      else:
+        hid = e.step(slots, data)
+        data = np.split(hid, np.cumsum(counts)[:-1], axis=0)
+    if not greedy:
+      ids = self._sample(logits)
+    self.stats["steps"] += 1
+    self.stats["rows"] += int(sum(counts))
+    still = []
+    for r, n, tok in zip(batch, counts, ids):
+      r.pos += n
+      if r.pos >= r.prompt.shape[1]:                 # the prompt's last row, or a decoded row: its output is a generated token
+        self._emit(r, int(tok))
+        r.last_token = int(tok)
+    for r in self.active:
+      if r.done:
+        for t in self.tables:
+          t.release(r.request_id)
+        self.reserved_pages -= self._pages(r.prompt.shape[1] + r.max_tokens)
+        self.finished[r.request_id] = r
+      else:
+        still.append(r)
+    self.active = still
+    return True
+
+  def run_until_idle(self) -> Dict[str, List[int]]:
+    while self.step() or self.pending():
+      pass
+    return {k: v.ids for k, v in self.finished.items()}
+
+
 class NodeTokenBridge:
   """on_token callback for ContinuousRing that delivers to a reference `Node` the way its own last-shard code does
   (node.py:127-137): `node.on_token.trigger_all(request_id, [token], is_finished)` ON THE EVENT-LOOP THREAD, and the
