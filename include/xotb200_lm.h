@@ -113,10 +113,13 @@ int xotb200_lm_step(xotb200_lm* e, int n_seq, const int32_t* slots, const int32_
  * out as [local layers, rows, width]. */
 int xotb200_lm_set_trace(xotb200_lm* e, int on);
 int xotb200_lm_read_trace(xotb200_lm* e, float* out, int64_t n_floats);
-/* Projection kernel choice: 0 = automatic (<= 8 rows: the one-warp-per-output decode kernel, else tiles), 1 = always tiles. */
+/* Projection kernel choice: 0 = automatic (<= 8 rows: the one-warp-per-output decode kernel; more rows: tcgen05 tensor-core tiles for
+ * bf16 operands that TMA can describe, else fp32 FMA tiles), 1 = always FMA tiles, 2 = tensor-core tiles at any row count. */
 int xotb200_lm_set_gemm_mode(xotb200_lm* e, int mode);
 
 int xotb200_lm_kernel_launches(xotb200_lm* e, int64_t* count);
+/* how many of the launches were tensor-core (tcgen05) products */
+int xotb200_lm_tensor_core_launches(xotb200_lm* e, int64_t* count);
 int xotb200_lm_weight_bytes(xotb200_lm* e, int64_t* bytes);
 int xotb200_lm_cache_stats(xotb200_lm* e, int* pages_total, int* pages_free, int* page_size);
 /* device time (CUDA events) of the most recent step, ms */

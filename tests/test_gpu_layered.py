@@ -324,3 +324,30 @@ def test_greedy_generation_through_the_batch_scheduler(dtype, budget):
   st = n.cache_stats()
   assert st["pages_free"] == st["pages_total"], "finished requests must give their pages back"
   n.close()
+
+
+# ---- the tensor-core products ------------------------------------------------------------------------------------------------------
+def test_tensor_core_products_equal_the_fma_tiles():
+  """sizes that TMA can describe (multiples of 8): prompts run their products on tcgen05, decoding on the one-warp-per-output
+  kernel; both must agree with the fp32-FMA tiles on the same 16-bit operands, and with the oracle"""
+  layers = [attn("latent_attention", heads=4, dim=16, rot_dim=8, vdim=24, kv_rank=40, q_rank=24, ff=72),
+            attn("latent_attention_2", heads=2, dim=8, rot_dim=8, vdim=8, kv_rank=16, window=70, ff=200),
+            delta(heads=2, dim=16, decay_rank=8, ff=0)]
+  cfg = config(layers, width=64, vocab=136, groups=4)
+  W = zo.random_weights(cfg, 12)
+  n = make_engine(cfg, W, "bfloat16", max_tokens=700, page_size=32)
+  toks = rand_tokens(cfg["vocab"], 300, 9)      # 300 rows: two full 128-row tiles and a ragged one
+  ref = oracle_logits(cfg, W, toks)[0]
+  before = n.tensor_core_launches()
+  tc = run_cut(n, 0, toks, [300])
+  used = n.tensor_core_launches() - before
+  assert used == 17, f"{used} of the prompt's 17 products ran on the tensor cores"
+  n.set_gemm_mode(1)
+  fma = run_cut(n, 1, toks, [300])
+  assert n.tensor_core_launches() - before == used
+  assert row_err(tc, ref) < TOL["bfloat16"] and row_err(fma, ref) < TOL["bfloat16"]
+  assert row_err(tc, fma.astype(np.float64)) < 0.02, "same operands, fp32 accumulation in both: only the summation order differs"
+  n.set_gemm_mode(2)                            # tensor cores also for a handful of rows
+  few = run_cut(n, 2, toks[:40], [5, 1])
+  assert row_err(few, ref[:40]) < TOL["bfloat16"]
+  n.close()

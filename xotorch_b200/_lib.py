@@ -138,6 +138,7 @@ _LM_SIGS = {
   "xotb200_lm_read_trace": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64]),
   "xotb200_lm_set_gemm_mode": (C.c_int, [C.c_void_p, C.c_int]),
   "xotb200_lm_kernel_launches": (C.c_int, [C.c_void_p, C.POINTER(C.c_int64)]),
+  "xotb200_lm_tensor_core_launches": (C.c_int, [C.c_void_p, C.POINTER(C.c_int64)]),
   "xotb200_lm_weight_bytes": (C.c_int, [C.c_void_p, C.POINTER(C.c_int64)]),
   "xotb200_lm_cache_stats": (C.c_int, [C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int)]),
   "xotb200_lm_last_step_ms": (C.c_int, [C.c_void_p, C.POINTER(C.c_float)]),

@@ -19,12 +19,14 @@
 #include <unistd.h>
 
 #include <algorithm>
+#include <type_traits>
 #include <map>
 #include <string>
 #include <vector>
 
 #include "../../include/xotb200_lm.h"
 #include "layered_kernels.cuh"
+#include "layered_tc.cuh"
 #include "st_header.h"
 
 using namespace xl;
@@ -65,6 +67,7 @@ struct Dest {
   size_t elem_off;   // element offset of the matrix in the blob
   int rows, cols, row_off;
   bool loaded;
+  int tr_heads = 0;   // > 0: the file's [heads * d, cols] matrix is stored head by head TRANSPOSED, [heads][cols][d]
 };
 
 struct LmLayer {
@@ -117,7 +120,9 @@ struct xotb200_lm {
   float* trace_buf = nullptr;
   size_t trace_floats = 0, trace_cap = 0;
   int gemm_mode = 0;
-  int64_t launches = 0;
+  int64_t launches = 0, tc_launches = 0;
+  int* d_err = nullptr;                                // sticky device error word (3 = a bounded wait of a tensor-core product expired)
+  int* h_err = nullptr;                                // pinned copy, read after every step
   float last_ms = 0.f;
 };
 
@@ -160,7 +165,8 @@ static int build_layout(xotb200_lm* e, const xotb200_lm_layer* all) {
       dest(p + "mix.dkv", L.w_in, R + dr, D, L.c_kv);
       if (s.out_gate) dest(p + "mix.g", L.w_in, H, D, L.c_g);
       L.dkv_norm = take(R); dest(p + "mix.dkv.norm", L.dkv_norm, 1, R, 0);
-      L.uk = take((size_t)H * dn * R); dest(p + "mix.uk", L.uk, H * dn, R, 0);
+      // W_uk is kept per head as [R, dn]: the absorption product q~ = W_uk[h]^T q then reads it K-major like every other weight
+      L.uk = take((size_t)H * dn * R); dest(p + "mix.uk", L.uk, H * dn, R, 0); e->dests[p + "mix.uk"].tr_heads = H;
       L.uv = take((size_t)H * dv * R); dest(p + "mix.uv", L.uv, H * dv, R, 0);
       L.wo = take((size_t)D * H * dv); dest(p + "mix.o", L.wo, D, H * dv, 0);
       e->max_q = std::max(e->max_q, HQ);
@@ -222,7 +228,11 @@ static int upload_tensor(xotb200_lm* e, Dest& d, const void* host_bf16) {
   if (er == cudaSuccess) {
     const int grid = (int)std::min<size_t>(4096, (n + 255) / 256);
     const size_t off = d.elem_off + (size_t)d.row_off * d.cols;
-    if (e->esz == 2) store_rows_kernel<bf16><<<grid, 256, 0, e->stream>>>(tmp, at<bf16>(e, off), n);
+    if (d.tr_heads > 0) {
+      const int dh = d.rows / d.tr_heads;
+      if (e->esz == 2) store_heads_transposed_kernel<bf16><<<grid, 256, 0, e->stream>>>(tmp, at<bf16>(e, off), d.tr_heads, dh, d.cols);
+      else store_heads_transposed_kernel<float><<<grid, 256, 0, e->stream>>>(tmp, at<float>(e, off), d.tr_heads, dh, d.cols);
+    } else if (e->esz == 2) store_rows_kernel<bf16><<<grid, 256, 0, e->stream>>>(tmp, at<bf16>(e, off), n);
     else store_rows_kernel<float><<<grid, 256, 0, e->stream>>>(tmp, at<float>(e, off), n);
     er = cudaGetLastError();
     e->launches++;
@@ -257,11 +267,69 @@ static int opt_in_smem(K kernel, size_t bytes) {
   return 0;
 }
 
+// ---- tensor-core path of the bf16 products (layered_tc.cuh) ---------------------------------------------------------------
+typedef CUresult (*encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                    const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static encode_tiled_fn get_encode_tiled() {
+  static encode_tiled_fn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<encode_tiled_fn>(p);
+  }
+  return fn;
+}
+// bf16 matrix [batch][rows, K] with row stride ld and batch stride bs (elements) as a 3-D map {K, rows, batch}, box {64, box_rows, 1},
+// 128-byte swizzle, zero fill outside.  False when the operand cannot be described (alignment) — the caller then uses the FMA tiles.
+static bool make_map3(CUtensorMap* m, const void* ptr, long rows, long K, long ld, long bs, int batch, int box_rows) {
+  encode_tiled_fn enc = get_encode_tiled();
+  if (!enc || (reinterpret_cast<uintptr_t>(ptr) & 15) || ld % 8 || (batch > 1 && bs % 8) || K < 1 || rows < 1) return false;
+  const cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)rows, (cuuint64_t)batch};
+  const cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)(batch > 1 ? bs : ld * rows) * 2};
+  const cuuint32_t box[3] = {(cuuint32_t)LTC_BK, (cuuint32_t)box_rows, 1};
+  const cuuint32_t es[3] = {1, 1, 1};
+  return enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int NT, int EPI, typename TC>
+static int launch_ltc(xotb200_lm* e, const CUtensorMap& ma, const CUtensorMap& mb, const LtcArgs& a, int batch) {
+  constexpr int NS = 3;
+  auto kern = ltc_gemm_kernel<NT, EPI, NS, TC>;
+  CK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ltc_smem_bytes(NT, NS)));
+  kern<<<dim3(cdiv(a.M, LTC_M), cdiv(a.N, NT), batch), LTC_THREADS, ltc_smem_bytes(NT, NS), e->stream>>>(ma, mb, a);
+  CK(cudaGetLastError());
+  e->launches++;
+  e->tc_launches++;
+  return 0;
+}
+
+// 1 = launched, 0 = not eligible (the caller falls back), < 0 = error
+template <typename TC, int EPI>
+static int product_tc(xotb200_lm* e, const bf16* A, long lda, long a_batch, const bf16* B, long ldb, long b_batch, TC* C, long ldc, long c_batch, int M,
+                      int N, int K, int batch) {
+  const int nt = N > 64 ? 128 : 64;
+  CUtensorMap ma, mb;
+  if (!make_map3(&ma, A, M, K, lda, a_batch, batch, LTC_M) || !make_map3(&mb, B, N, K, ldb, b_batch, batch, nt)) return 0;
+  LtcArgs a{M, N, K, C, ldc, c_batch, e->d_err};
+  if (nt == 128) TRY((launch_ltc<128, EPI, TC>(e, ma, mb, a, batch)));
+  else TRY((launch_ltc<64, EPI, TC>(e, ma, mb, a, batch)));
+  return 1;
+}
+
 template <typename TA, typename TB, typename TC, int EPI>
 static int product(xotb200_lm* e, const TA* A, long lda, long a_batch, const TB* B, long sbn, long sbk, long b_batch, TC* C, long ldc, long c_batch,
                    int M, int N, int K, int batch) {
   if (M == 0 || N == 0) return 0;
   const size_t smem = (size_t)M * K * 4;
+  if constexpr (std::is_same<TA, bf16>::value && std::is_same<TB, bf16>::value && (EPI == 0 || !std::is_same<TC, float>::value)) {
+    // 16-bit operands with more rows than the decode kernel takes: the tensor cores, when the operands can be described to TMA
+    if (sbk == 1 && ((e->gemm_mode == 0 && M > 8) || e->gemm_mode == 2)) {
+      const int r = product_tc<TC, EPI>(e, A, lda, a_batch, B, sbn, b_batch, C, ldc, c_batch, M, N, K, batch);
+      if (r != 0) return r < 0 ? r : 0;
+    }
+  }
   if (e->gemm_mode == 0 && M <= 8 && sbk == 1 && smem <= GEMV_SMEM_MAX) {
     auto kern = gemv_rows_kernel<TA, TB, TC, EPI, 8>;
     TRY(opt_in_smem(kern, smem));
@@ -366,7 +434,7 @@ static int attention_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
   CK(cudaGetLastError());
   e->launches += 2;
   // key absorption: qfull[m, h, 0:R] = sum_d qn[m, h, d] * W_uk[h * dn + d, :]
-  TRY((product<T, T, float, 0>(e, static_cast<T*>(e->qn), (long)H * dn, dn, at<T>(e, L.uk), 1, R, (long)dn * R, e->qfull, (long)H * (R + dr), R + dr, M, R,
+  TRY((product<T, T, float, 0>(e, static_cast<T*>(e->qn), (long)H * dn, dn, at<T>(e, L.uk), dn, 1, (long)dn * R, e->qfull, (long)H * (R + dr), R + dr, M, R,
                                dn, H)));
   {
     const int qpi = std::max(1, 32 / H);
@@ -536,6 +604,12 @@ int xotb200_lm_create(const xotb200_lm_cfg* cfg, const xotb200_lm_layer* layers,
     return fail(XOTB200_ECUDA);
   }
   cudaMemsetAsync(e->blob, 0, e->blob_elems * e->esz, e->stream);
+  if (cudaMalloc(&e->d_err, 4) != cudaSuccess || cudaHostAlloc(&e->h_err, 4, cudaHostAllocDefault) != cudaSuccess) {
+    set_err("allocation of the error word failed");
+    return fail(XOTB200_ECUDA);
+  }
+  cudaMemsetAsync(e->d_err, 0, 4, e->stream);
+  *e->h_err = 0;
   for (auto& L : e->layers) {
     if (L.s.mixer != XOTB200_LM_MIX_LATENT_ATTN || L.s.rot_dims == 0) continue;
     std::vector<float> f(L.s.rot_dims / 2);
@@ -565,6 +639,8 @@ int xotb200_lm_destroy(xotb200_lm* e) {
     if (p) cudaFree(p);
   if (e->h_stage) cudaFreeHost(e->h_stage);
   if (e->h_out) cudaFreeHost(e->h_out);
+  if (e->h_err) cudaFreeHost(e->h_err);
+  if (e->d_err) cudaFree(e->d_err);
   if (e->ev0) cudaEventDestroy(e->ev0);
   if (e->ev1) cudaEventDestroy(e->ev1);
   if (e->stream) cudaStreamDestroy(e->stream);
@@ -821,9 +897,14 @@ int xotb200_lm_step(xotb200_lm* e, int n_seq, const int32_t* slots, const int32_
     TRY(ensure_host_out(e, (size_t)M * D));
     CK(cudaMemcpyAsync(e->h_out, e->x, (size_t)M * D * 4, cudaMemcpyDeviceToHost, e->stream));
   }
+  CK(cudaMemcpyAsync(e->h_err, e->d_err, 4, cudaMemcpyDeviceToHost, e->stream));
   CK(cudaEventRecord(e->ev1, e->stream));
   CK(cudaStreamSynchronize(e->stream));
   CK(cudaEventElapsedTime(&e->last_ms, e->ev0, e->ev1));
+  if (*e->h_err != 0) {
+    set_err("a kernel gave up a bounded wait (device error word %d); the step's results are not valid", *e->h_err);
+    return XOTB200_ECUDA;
+  }
   if (e->last && n_want > 0) {
     if (logits_f32) memcpy(logits_f32, e->h_out, (size_t)n_want * V * 4);
     if (argmax_i32) memcpy(argmax_i32, e->h_out + (size_t)n_want * V, (size_t)n_want * 4);
@@ -851,7 +932,7 @@ int xotb200_lm_read_trace(xotb200_lm* e, float* out, int64_t n_floats) {
 }
 
 int xotb200_lm_set_gemm_mode(xotb200_lm* e, int mode) {
-  REQUIRE(e && mode >= 0 && mode <= 1, "gemm mode must be 0 or 1");
+  REQUIRE(e && mode >= 0 && mode <= 2, "gemm mode must be 0, 1 or 2");
   e->gemm_mode = mode;
   return 0;
 }
@@ -859,6 +940,12 @@ int xotb200_lm_set_gemm_mode(xotb200_lm* e, int mode) {
 int xotb200_lm_kernel_launches(xotb200_lm* e, int64_t* count) {
   REQUIRE(e && count, "null argument");
   *count = e->launches;
+  return 0;
+}
+
+int xotb200_lm_tensor_core_launches(xotb200_lm* e, int64_t* count) {
+  REQUIRE(e && count, "null argument");
+  *count = e->tc_launches;
   return 0;
 }
 

@@ -518,6 +518,16 @@ __global__ void store_rows_kernel(const bf16* __restrict__ src, T* __restrict__ 
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
     stf(dst + i, __bfloat162float(src[i]));
 }
+// src [heads * d, cols] (row-major, bf16 bits) -> dst [heads][cols][d]: each head's block transposed
+template <typename T>
+__global__ void store_heads_transposed_kernel(const bf16* __restrict__ src, T* __restrict__ dst, int heads, int d, int cols) {
+  const size_t n = (size_t)heads * d * cols;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t h = i / ((size_t)d * cols), r = i % ((size_t)d * cols);
+    const size_t c = r / d, k = r % d;
+    stf(dst + i, __bfloat162float(src[(h * d + k) * cols + c]));
+  }
+}
 __global__ void copy_rows_f32_kernel(const float* __restrict__ src, float* __restrict__ dst, int ld_src, int ld_dst, int n, int M) {
   const size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
   if (i >= (size_t)M * n) return;

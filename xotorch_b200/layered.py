@@ -281,6 +281,11 @@ class LayeredShard:
     check_lm(self.lib.xotb200_lm_kernel_launches(self.h, C.byref(v)))
     return int(v.value)
 
+  def tensor_core_launches(self) -> int:
+    v = C.c_int64()
+    check_lm(self.lib.xotb200_lm_tensor_core_launches(self.h, C.byref(v)))
+    return int(v.value)
+
   def weight_bytes(self) -> int:
     v = C.c_int64()
     check_lm(self.lib.xotb200_lm_weight_bytes(self.h, C.byref(v)))
