@@ -487,7 +487,15 @@ def main():
   ap.add_argument("--model", default=MODEL, choices=sorted(k for k in PRESETS if not k.startswith("tiny")))
   ap.add_argument("--prompt", type=int, default=N_PROMPT)
   ap.add_argument("--gen", type=int, default=N_GEN)
+  # the layered engine (models given as a list of layers: latent attention, delta rule) beside a Llama decoder of equal size;
+  # an option of its own: the default workload above and its JSON line are untouched
+  ap.add_argument("--layered", action="store_true", help="prefill / decode throughput of Zokuvik-shaped models next to a Llama of the same size")
+  ap.add_argument("--layered-sizes", default="", help="comma list out of small,medium,large (default: all)")
+  ap.add_argument("--layered-prompts", default="", help="prompt lengths (default 1024,4096)")
   args = ap.parse_args()
+  if args.layered:
+    from xotorch_b200.bench_layered import run as run_layered
+    return run_layered(args)
   globals().update(MODEL=args.model, N_PROMPT=args.prompt, N_GEN=args.gen)
   if args.impl == "reference":
     run_reference(args)

@@ -91,6 +91,8 @@ int xotb200_lm_load_dir(xotb200_lm* e, const char* dir);
 /* one tensor from host memory as bf16 bit patterns; returns 1 when the tensor belongs to another shard (ignored) */
 int xotb200_lm_load_tensor(xotb200_lm* e, const char* name, const void* bf16_bits, const int64_t* shape, int ndim);
 int xotb200_lm_check_loaded(xotb200_lm* e);
+/* random weights made on the device (benchmarks, smoke runs): matrices ~ U with deviation 1/sqrt(inputs), norm weights near 1 */
+int xotb200_lm_init_synthetic(xotb200_lm* e, uint64_t seed);
 
 /* Request state: (re)creates the cache for at most max_requests live requests holding at most max_tokens tokens together.
  * page_size tokens per page (0 = 64).  All slots start empty. */
@@ -118,6 +120,10 @@ int xotb200_lm_read_trace(xotb200_lm* e, float* out, int64_t n_floats);
 int xotb200_lm_set_gemm_mode(xotb200_lm* e, int mode);
 
 int xotb200_lm_kernel_launches(xotb200_lm* e, int64_t* count);
+/* Attention kernel choice in the bf16 mode: 0 = automatic (a request that brings 16 rows or more: expanded keys / values and the
+ * tensor-core streaming-softmax kernel; fewer rows: the absorbed kernel over the latent rows), 1 = always the absorbed kernel. */
+int xotb200_lm_set_attention_mode(xotb200_lm* e, int mode);
+int xotb200_lm_prompt_attention_launches(xotb200_lm* e, int64_t* count);
 /* how many of the launches were tensor-core (tcgen05) products */
 int xotb200_lm_tensor_core_launches(xotb200_lm* e, int64_t* count);
 int xotb200_lm_weight_bytes(xotb200_lm* e, int64_t* bytes);

@@ -351,3 +351,37 @@ def test_tensor_core_products_equal_the_fma_tiles():
   few = run_cut(n, 2, toks[:40], [5, 1])
   assert row_err(few, ref[:40]) < TOL["bfloat16"]
   n.close()
+
+
+# ---- prompt attention in the expanded form -----------------------------------------------------------------------------------------
+@pytest.mark.parametrize("sizes", ["aligned", "odd"])
+def test_expanded_prompt_attention_equals_the_absorbed_kernel(sizes):
+  """bf16: a request that brings 16 rows or more has its keys and values expanded and runs the tensor-core streaming-softmax
+  kernel; fewer rows run the absorbed kernel over the latent rows.  Same design, two kernels: they agree with each other and
+  with the oracle — across 64-row tiles, second portions that start inside a window, gated and windowed mixers, in one batch
+  with short requests."""
+  if sizes == "aligned":
+    layers = [attn("latent_attention", heads=4, dim=16, rot_dim=8, vdim=24, kv_rank=40, q_rank=24, ff=0),
+              attn("latent_attention_2", heads=2, dim=32, rot_dim=16, vdim=72, kv_rank=64, window=70, ff=64)]
+  else:
+    layers = [attn("latent_attention", heads=3, dim=10, rot_dim=6, vdim=5, kv_rank=21, q_rank=9, ff=0),
+              attn("latent_attention_2", heads=5, dim=7, rot_dim=4, vdim=9, kv_rank=12, window=37, ff=20)]
+  cfg = config(layers, width=64 if sizes == "aligned" else 40, vocab=90, groups=4)
+  W = zo.random_weights(cfg, 14)
+  n = make_engine(cfg, W, "bfloat16", max_tokens=1200, max_requests=4, page_size=16)
+  a, b, c = rand_tokens(90, 333, 1), rand_tokens(90, 150, 2), rand_tokens(90, 9, 3)
+  ra, rb, rc = (oracle_logits(cfg, W, t)[0] for t in (a, b, c))
+  before = n.prompt_attention_launches()
+  # step 1: a's first 200 rows, all of b and all of c (short: absorbed) in one batch;  step 2: the rest of a (133 rows, starts at 200)
+  lg1, _ = n.step([0, 1, 2], [a[:200], b, c], want=list(range(200 + 150 + 9)))
+  lg2, _ = n.step([0], [a[200:]], want=list(range(133)))
+  assert n.prompt_attention_launches() - before == 4
+  got_a = np.concatenate([lg1[:200], lg2])
+  for got, ref, who in ((got_a, ra, "a"), (lg1[200:350], rb, "b"), (lg1[350:], rc, "c")):
+    assert row_err(got, ref) < TOL["bfloat16"], who
+  n.set_attention_mode(1)
+  n.clear_request(0)
+  absorbed = run_cut(n, 0, a, [200, 133])
+  assert n.prompt_attention_launches() - before == 4
+  assert row_err(got_a, absorbed.astype(np.float64)) < 0.03
+  n.close()

@@ -129,6 +129,7 @@ _LM_SIGS = {
   "xotb200_lm_load_dir": (C.c_int, [C.c_void_p, C.c_char_p]),
   "xotb200_lm_load_tensor": (C.c_int, [C.c_void_p, C.c_char_p, C.c_void_p, C.POINTER(C.c_int64), C.c_int]),
   "xotb200_lm_check_loaded": (C.c_int, [C.c_void_p]),
+  "xotb200_lm_init_synthetic": (C.c_int, [C.c_void_p, C.c_uint64]),
   "xotb200_lm_begin": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int]),
   "xotb200_lm_clear_request": (C.c_int, [C.c_void_p, C.c_int]),
   "xotb200_lm_request_len": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_int)]),
@@ -138,6 +139,8 @@ _LM_SIGS = {
   "xotb200_lm_read_trace": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64]),
   "xotb200_lm_set_gemm_mode": (C.c_int, [C.c_void_p, C.c_int]),
   "xotb200_lm_kernel_launches": (C.c_int, [C.c_void_p, C.POINTER(C.c_int64)]),
+  "xotb200_lm_set_attention_mode": (C.c_int, [C.c_void_p, C.c_int]),
+  "xotb200_lm_prompt_attention_launches": (C.c_int, [C.c_void_p, C.POINTER(C.c_int64)]),
   "xotb200_lm_tensor_core_launches": (C.c_int, [C.c_void_p, C.POINTER(C.c_int64)]),
   "xotb200_lm_weight_bytes": (C.c_int, [C.c_void_p, C.POINTER(C.c_int64)]),
   "xotb200_lm_cache_stats": (C.c_int, [C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int)]),

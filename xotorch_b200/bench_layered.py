@@ -1,0 +1,165 @@
+"""`bench.py --layered`: prefill and decode throughput of the layered engine on Zokuvik-shaped models with random weights, at a
+few sizes that resemble a real model's layers, beside the shard engine's Llama decoder of the same width, depth and (to a few
+per cent) weight bytes.  One JSON line per size; nothing here touches bench.py's default workload.
+
+Timing: every number is the device time of the step(s) (CUDA events on the engine's stream, `last_step_ms` / the ring's own
+timer), after warm-up; the weights of every size are larger than L2 from `medium` on, and each prompt step streams all of them.
+Roofline denominators come from MEASURED_PEAKS.json (fallback: the profiling recipe's numbers)."""
+from __future__ import annotations
+
+import json
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent.parent
+
+# width, layer pattern repeats, attention heads / dn / dr / dv / latent ranks, delta heads x dim, ff, vocab
+SIZES = {
+  "small": dict(width=1024, repeats=2, heads=8, dim=64, rot_dim=32, vdim=64, kv_rank=256, q_rank=384, dheads=16, ddim=64, ff=4096, vocab=32000),
+  "medium": dict(width=2048, repeats=2, heads=16, dim=128, rot_dim=64, vdim=128, kv_rank=512, q_rank=768, dheads=32, ddim=64, ff=8192, vocab=32000),
+  "large": dict(width=4096, repeats=2, heads=32, dim=128, rot_dim=64, vdim=128, kv_rank=512, q_rank=1536, dheads=32, ddim=128, ff=14336, vocab=32000),
+}
+WINDOW, DECAY_RANK = 1024, 64
+
+
+def zokuvik_config(s: dict):
+  def att(kind):
+    m = {"heads": s["heads"], "dim": s["dim"], "rot_dim": s["rot_dim"], "vdim": s["vdim"], "kv_rank": s["kv_rank"],
+         "rot": {"base": 10000.0, "dims": s["rot_dim"]}, "scale": float((s["dim"] + s["rot_dim"]) ** -0.5)}
+    if kind == "latent_attention":
+      m["q_rank"] = s["q_rank"]
+    else:
+      m["mask"] = {"size": WINDOW}
+    return {"type": kind, "mixer": m, "mlp": {"kind": "dense", "ff": s["ff"]}}
+  layers = []
+  for _ in range(s["repeats"]):
+    layers += [att("latent_attention"), att("latent_attention_2"),
+               {"type": "general_delta", "mixer": {"heads": s["dheads"], "dim": s["ddim"]}, "mlp": {"kind": "dense", "ff": s["ff"]}}]
+  cfg = {"architecture": "Zokuvik", "width": s["width"], "vocab": s["vocab"], "norm": {"eps": 1e-6, "groups": 4}, "layers": layers}
+  shapes = {f"l{i}.mix.w1": (DECAY_RANK, s["width"]) for i, l in enumerate(layers) if l["type"] == "general_delta"}
+  return cfg, shapes
+
+
+def peaks():
+  p = ROOT / "MEASURED_PEAKS.json"
+  if p.exists():
+    try:
+      d = json.loads(p.read_text())
+      return float(d["hbm_gbs"]), float(d.get("bf16_tflops", 1590.0)), "measured"
+    except Exception:
+      pass
+  return 6650.0, 1590.0, "fallback"
+
+
+def layered_numbers(s: dict, prompts, decode_ctx: int, decode_batches, steps: int, warmup: int) -> dict:
+  from .layered import LayeredShard
+  cfg, shapes = zokuvik_config(s)
+  eng = LayeredShard(cfg, 0, "bfloat16")
+  eng.set_shard(0, len(cfg["layers"]) - 1, shapes)
+  eng.init_synthetic(7)
+  wbytes = eng.weight_bytes()
+  body = wbytes - 2 * s["vocab"] * s["width"]                       # a prompt step streams the body once + one row of the embedding per token
+  rng = np.random.default_rng(0)
+  out = {"weight_bytes": wbytes, "prefill": {}, "decode": {}}
+  max_b = max(decode_batches)
+  eng.begin_pool(max(max(prompts), (decode_ctx + steps + warmup + 8) * max_b) + 64, max_b)
+  launches0 = eng.kernel_launches()
+  for n in prompts:
+    toks = rng.integers(0, s["vocab"], size=n).astype(np.int32)
+    ms = []
+    for it in range(warmup + steps):
+      eng.clear_request(0)
+      eng.step([0], [toks])
+      if it >= warmup:
+        ms.append(eng.last_step_ms())
+    t = float(np.median(ms))
+    out["prefill"][str(n)] = {"ms": round(t, 3), "tok_s": round(n / t * 1e3, 1), "tflops_weights": round(2 * (body / 2) * n / t / 1e9, 1)}
+  for b in decode_batches:
+    for sl in range(max_b):
+      eng.clear_request(sl)
+    ctx = rng.integers(0, s["vocab"], size=(b, decode_ctx)).astype(np.int32)
+    eng.step(list(range(b)), [ctx[i] for i in range(b)])
+    ms, wall = [], []
+    for it in range(warmup + steps * 8):
+      t0 = time.perf_counter()
+      eng.step(list(range(b)), [rng.integers(0, s["vocab"], size=1).astype(np.int32) for _ in range(b)])
+      if it >= warmup:
+        wall.append((time.perf_counter() - t0) * 1e3)
+        ms.append(eng.last_step_ms())
+    t, tw = float(np.median(ms)), float(np.median(wall))
+    stream = body + s["vocab"] * s["width"] * 2                      # body + the head matrix per step
+    out["decode"][str(b)] = {"ms_device": round(t, 4), "ms_wall": round(tw, 4), "tok_s": round(b / tw * 1e3, 1),
+                             "gbs_weights_device": round(stream / t / 1e6, 1)}
+  out["kernel_launches"] = eng.kernel_launches() - launches0
+  out["tensor_core_launches"] = eng.tensor_core_launches()
+  eng.close()
+  return out
+
+
+def llama_numbers(s: dict, target_bytes: int, prompts, decode_ctx: int, steps: int, warmup: int) -> dict:
+  """the shard engine on a Llama decoder of the same width and depth; its feed-forward size is chosen so that the weight bytes
+  match the layered model's"""
+  from .native import NativeShard
+  from .synth import ModelShape, hf_config
+  D, L, V = s["width"], 3 * s["repeats"], s["vocab"]
+  hd = 128 if D >= 2048 else 64
+  H = D // hd
+  Hkv = max(1, H // 4)
+  attn_params = D * (H + 2 * Hkv) * hd + H * hd * D
+  per_layer = (target_bytes / 2 - 2 * V * D) / L
+  ffn = int(max(512, (per_layer - attn_params) / (3 * D)) // 512 * 512)       # the shard engine wants multiples of 512
+  shape = ModelShape("bench", L, D, ffn, H, Hkv, hd, V, max_pos=max(max(prompts), decode_ctx + 4096) + 64)
+  eng = NativeShard(hf_config(shape), device=0)
+  eng.set_shard(0, L - 1)
+  eng.init_synthetic(7)
+  rng = np.random.default_rng(0)
+  out = {"weight_bytes": eng.weight_bytes(), "ffn": ffn, "prefill": {}, "decode": {}}
+  body = out["weight_bytes"] - 2 * V * D
+  for n in prompts:
+    toks = rng.integers(0, V, size=(1, n)).astype(np.int32)
+    ms = []
+    for it in range(warmup + steps):
+      eng.begin_request(n + 8)
+      t0 = time.perf_counter()
+      eng.forward(toks, 0)
+      if it >= warmup:
+        ms.append((time.perf_counter() - t0) * 1e3)
+    t = float(np.median(ms))
+    out["prefill"][str(n)] = {"ms_wall": round(t, 3), "tok_s": round(n / t * 1e3, 1), "tflops_weights": round(2 * (body / 2) * n / t / 1e9, 1)}
+  n_dec = 64
+  eng.link_next_local(eng)
+  eng.begin_request(decode_ctx + (warmup + steps) * n_dec + 8)
+  eng.forward(rng.integers(0, V, size=(1, decode_ctx)).astype(np.int32), 0)
+  eng.post_to_next(0)
+  ms, step0, pos = [], 0, decode_ctx
+  for it in range(warmup + steps):
+    eng.ring_launch(n_dec, step0, pos)
+    _, t = eng.ring_wait(n_dec)
+    step0 += n_dec
+    pos += n_dec
+    if it >= warmup:
+      ms.append(t / n_dec)
+  t = float(np.median(ms))
+  out["decode"]["1"] = {"ms_device": round(t, 4), "tok_s": round(1e3 / t, 1), "gbs_weights_device": round((body + V * D * 2) / t / 1e6, 1)}
+  eng.close()
+  return out
+
+
+def run(args) -> None:
+  hbm, tf, src = peaks()
+  sizes = [x for x in (args.layered_sizes or "small,medium,large").split(",") if x]
+  prompts = [int(x) for x in (args.layered_prompts or "1024,4096").split(",")]
+  for name in sizes:
+    s = SIZES[name]
+    z = layered_numbers(s, prompts, decode_ctx=1024, decode_batches=[1, 8], steps=args.steps, warmup=max(3, args.warmup))
+    l = llama_numbers(s, z["weight_bytes"], prompts, decode_ctx=1024, steps=args.steps, warmup=max(3, args.warmup))
+    line = {"bench": "layered", "size": name, "dtype": "bf16", "data": "synthetic", "shape": s, "zokuvik": z, "llama_same_size": l,
+            "peaks": {"hbm_gbs": hbm, "bf16_tflops": tf, "source": src},
+            "frac_of_peak": {
+              "zokuvik_decode1_hbm": round(z["decode"]["1"]["gbs_weights_device"] / hbm, 3),
+              "llama_decode1_hbm": round(l["decode"]["1"]["gbs_weights_device"] / hbm, 3),
+              **{f"zokuvik_prefill{n}_tensor": round(z["prefill"][str(n)]["tflops_weights"] / tf, 3) for n in prompts},
+              **{f"llama_prefill{n}_tensor": round(l["prefill"][str(n)]["tflops_weights"] / tf, 3) for n in prompts}}}
+    print(json.dumps(line), flush=True)

@@ -67,6 +67,8 @@ struct Dest {
   size_t elem_off;   // element offset of the matrix in the blob
   int rows, cols, row_off;
   bool loaded;
+  bool has2 = false;  // a second, untransposed copy at elem_off2 (W_uk: the expanded prompt attention reads it row-major)
+  size_t elem_off2 = 0;
   int tr_heads = 0;   // > 0: the file's [heads * d, cols] matrix is stored head by head TRANSPOSED, [heads][cols][d]
 };
 
@@ -76,7 +78,7 @@ struct LmLayer {
   size_t w_in;                                         // concatenated input projections [n_in, D]
   int n_in;
   int c_q, c_kv, c_g;                                  // latent attention: columns of the projection output
-  size_t dq_norm, uq, dkv_norm, uk, uv, wo;
+  size_t dq_norm, uq, dkv_norm, uk, uk_rows, uv, wo;
   int c_r, c_k, c_v, c_a, c_w1;                        // delta rule: columns (gate shares c_g)
   size_t w2, w0, a_b, onorm;
   size_t up, down;
@@ -112,6 +114,9 @@ struct xotb200_lm {
   int m_cap = 0, want_cap = 0;
   float *x = nullptr, *y = nullptr, *proj = nullptr, *qraw = nullptr, *qfull = nullptr, *wlog = nullptr, *oraw = nullptr, *logits = nullptr;
   void *h = nullptr, *cqn = nullptr, *qn = nullptr, *olat = nullptr, *oh = nullptr, *act = nullptr, *th = nullptr, *hw = nullptr;
+  void *q16 = nullptr, *cbuf = nullptr, *knx = nullptr, *vxx = nullptr;   // expanded prompt attention (bf16)
+  size_t flash_keys_cap = 0;
+  int max_w = 0;                                       // widest cached row (kv_rank + rot_dim)
   int* d_argmax = nullptr;
   float* h_out = nullptr;                              // pinned staging for results
   size_t h_out_cap = 0;
@@ -120,7 +125,9 @@ struct xotb200_lm {
   float* trace_buf = nullptr;
   size_t trace_floats = 0, trace_cap = 0;
   int gemm_mode = 0;
-  int64_t launches = 0, tc_launches = 0;
+  bool flash_on = true;                                // bf16: prompt portions of FLASH_MIN_ROWS rows or more use the expanded tensor-core attention
+  std::vector<int> stage_build;
+  int64_t launches = 0, tc_launches = 0, flash_launches = 0;
   int* d_err = nullptr;                                // sticky device error word (3 = a bounded wait of a tensor-core product expired)
   int* h_err = nullptr;                                // pinned copy, read after every step
   float last_ms = 0.f;
@@ -167,6 +174,7 @@ static int build_layout(xotb200_lm* e, const xotb200_lm_layer* all) {
       L.dkv_norm = take(R); dest(p + "mix.dkv.norm", L.dkv_norm, 1, R, 0);
       // W_uk is kept per head as [R, dn]: the absorption product q~ = W_uk[h]^T q then reads it K-major like every other weight
       L.uk = take((size_t)H * dn * R); dest(p + "mix.uk", L.uk, H * dn, R, 0); e->dests[p + "mix.uk"].tr_heads = H;
+      L.uk_rows = take((size_t)H * dn * R); e->dests[p + "mix.uk"].has2 = true; e->dests[p + "mix.uk"].elem_off2 = L.uk_rows;
       L.uv = take((size_t)H * dv * R); dest(p + "mix.uv", L.uv, H * dv, R, 0);
       L.wo = take((size_t)D * H * dv); dest(p + "mix.o", L.wo, D, H * dv, 0);
       e->max_q = std::max(e->max_q, HQ);
@@ -175,6 +183,7 @@ static int build_layout(xotb200_lm* e, const xotb200_lm_layer* all) {
       e->max_hdn = std::max(e->max_hdn, H * dn);
       e->max_olat = std::max(e->max_olat, H * R);
       e->max_oh = std::max(e->max_oh, H * dv);
+      e->max_w = std::max(e->max_w, R + dr);
     } else if (s.mixer == XOTB200_LM_MIX_DELTA_RULE) {
       const int HD = s.heads * s.dim;
       REQUIRE(s.vdim == s.dim, "layer %d: the delta rule uses one size for keys and values", li);
@@ -234,6 +243,11 @@ static int upload_tensor(xotb200_lm* e, Dest& d, const void* host_bf16) {
       else store_heads_transposed_kernel<float><<<grid, 256, 0, e->stream>>>(tmp, at<float>(e, off), d.tr_heads, dh, d.cols);
     } else if (e->esz == 2) store_rows_kernel<bf16><<<grid, 256, 0, e->stream>>>(tmp, at<bf16>(e, off), n);
     else store_rows_kernel<float><<<grid, 256, 0, e->stream>>>(tmp, at<float>(e, off), n);
+    if (d.has2) {
+      if (e->esz == 2) store_rows_kernel<bf16><<<grid, 256, 0, e->stream>>>(tmp, at<bf16>(e, d.elem_off2), n);
+      else store_rows_kernel<float><<<grid, 256, 0, e->stream>>>(tmp, at<float>(e, d.elem_off2), n);
+      e->launches++;
+    }
     er = cudaGetLastError();
     e->launches++;
   }
@@ -368,6 +382,7 @@ static int ensure_scratch(xotb200_lm* e, int M, int n_want) {
     TRY(regrow(e->h, m * D * z));
     TRY(regrow(e->cqn, m * e->max_qr * z));
     TRY(regrow(e->qn, m * e->max_hdn * z));
+    if (z == 2) TRY(regrow(e->q16, m * e->max_q * 2));
     TRY(regrow(e->olat, m * e->max_olat * z));
     TRY(regrow(e->oh, m * e->max_oh * z));
     TRY(regrow(e->act, m * e->max_ff * z));
@@ -405,6 +420,14 @@ struct StepPlan {
   const int *tokens = nullptr, *row_slot = nullptr, *row_pos = nullptr, *want = nullptr;   // device
   const Item* seqs = nullptr;
   std::map<int, std::pair<const Item*, int>> items;   // rows per attention work item -> (device list, count)
+  // expanded prompt attention (bf16): per distinct window of the model's attention layers, the requests that bring many rows
+  struct Flash {
+    const GatherReq* reqs = nullptr;
+    const FlashTile* tiles = nullptr;
+    int n_reqs = 0, n_tiles = 0, n_keys = 0, max_keys = 0;
+  };
+  std::map<int, Flash> flash;
+  bool any_short = true;                               // some request goes through the absorbed kernel
 };
 
 template <typename T>
@@ -429,20 +452,30 @@ static int attention_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
   latent_append_kernel<T><<<cdiv(M, 8), 256, 0, e->stream>>>(e->proj, L.n_in, L.c_kv, R, dr, at<T>(e, L.dkv_norm), eps, L.freqs, s.rot_dims, s.rot_layout,
                                                              sp.row_slot, sp.row_pos, pg, static_cast<T*>(L.pool), M);
   CK(cudaGetLastError());
-  query_split_kernel<T><<<cdiv((long)M * H, 8), 256, 0, e->stream>>>(qraw, q_ld, 0, H, dn, dr, R, L.freqs, s.rot_dims, s.rot_layout, sp.row_pos,
-                                                                      static_cast<T*>(e->qn), e->qfull, M);
-  CK(cudaGetLastError());
-  e->launches += 2;
-  // key absorption: qfull[m, h, 0:R] = sum_d qn[m, h, d] * W_uk[h * dn + d, :]
-  TRY((product<T, T, float, 0>(e, static_cast<T*>(e->qn), (long)H * dn, dn, at<T>(e, L.uk), dn, 1, (long)dn * R, e->qfull, (long)H * (R + dr), R + dr, M, R,
-                               dn, H)));
-  {
+  e->launches++;
+  // ---- which rows take which form
+  const StepPlan::Flash* fl = nullptr;
+  if constexpr (std::is_same<T, bf16>::value) {
+    auto f = sp.flash.find(s.window);
+    const int dqp = (dn + dr + 15) & ~15;
+    if (f != sp.flash.end() && f->second.n_tiles > 0 && dv <= 128 && dqp <= 256) fl = &f->second;
+  }
+  const float* gate = s.out_gate ? e->proj : nullptr;
+  if (sp.any_short || !fl) {
+    // absorbed form (few rows per request, and everything in the 32-bit mode)
+    query_split_kernel<T><<<cdiv((long)M * H, 8), 256, 0, e->stream>>>(qraw, q_ld, 0, H, dn, dr, R, L.freqs, s.rot_dims, s.rot_layout, sp.row_pos,
+                                                                        static_cast<T*>(e->qn), e->qfull, M);
+    CK(cudaGetLastError());
+    e->launches++;
+    // key absorption: qfull[m, h, 0:R] = sum_d qn[m, h, d] * W_uk[h][:, d]
+    TRY((product<T, T, float, 0>(e, static_cast<T*>(e->qn), (long)H * dn, dn, at<T>(e, L.uk), dn, 1, (long)dn * R, e->qfull, (long)H * (R + dr), R + dr, M, R,
+                                 dn, H)));
     const int qpi = std::max(1, 32 / H);
     const auto& it = sp.items.at(qpi);
-    const int pairs = qpi * H, nw = std::min(32, pairs);
-    const size_t smem = ((size_t)32 * ((R + dr) | 1) + (size_t)nw * (R + dr)) * 4;
-    const float* gate = s.out_gate ? e->proj : nullptr;
-    const dim3 grid(it.second, cdiv(pairs, nw));
+    if (it.second > 0) {
+      const int pairs = qpi * H, nw = std::min(32, pairs);
+      const size_t smem = ((size_t)32 * ((R + dr) | 1) + (size_t)nw * (R + dr)) * 4;
+      const dim3 grid(it.second, cdiv(pairs, nw));
 #define LAUNCH_ATTN(NACC)                                                                                                                       \
   do {                                                                                                                                          \
     auto kern = latent_attention_kernel<T, NACC>;                                                                                               \
@@ -450,17 +483,47 @@ static int attention_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
     kern<<<grid, nw * 32, smem, e->stream>>>(e->qfull, static_cast<const T*>(L.pool), pg, it.first, H, R, dr, s.scale, s.window, gate, L.n_in, \
                                              L.c_g, static_cast<T*>(e->olat));                                                                  \
   } while (0)
-    if (R <= 64) LAUNCH_ATTN(2);
-    else if (R <= 128) LAUNCH_ATTN(4);
-    else if (R <= 256) LAUNCH_ATTN(8);
-    else LAUNCH_ATTN(16);
+      if (R <= 64) LAUNCH_ATTN(2);
+      else if (R <= 128) LAUNCH_ATTN(4);
+      else if (R <= 256) LAUNCH_ATTN(8);
+      else LAUNCH_ATTN(16);
 #undef LAUNCH_ATTN
-    CK(cudaGetLastError());
-    e->launches++;
+      CK(cudaGetLastError());
+      e->launches++;
+    }
+    // value expansion per head
+    TRY((product<T, T, T, 0>(e, static_cast<T*>(e->olat), (long)H * R, R, at<T>(e, L.uv), R, 1, (long)dv * R, static_cast<T*>(e->oh), (long)H * dv, dv, M, dv,
+                             R, H)));
   }
-  // value expansion per head, then the output projection
-  TRY((product<T, T, T, 0>(e, static_cast<T*>(e->olat), (long)H * R, R, at<T>(e, L.uv), R, 1, (long)dv * R, static_cast<T*>(e->oh), (long)H * dv, dv, M, dv,
-                           R, H)));
+  if constexpr (std::is_same<T, bf16>::value) {
+    if (fl) {
+      // expanded form for the requests that bring many rows (it overwrites their rows of `oh`)
+      bf16 *q16 = static_cast<bf16*>(e->q16), *cbuf = static_cast<bf16*>(e->cbuf), *knx = static_cast<bf16*>(e->knx), *vxx = static_cast<bf16*>(e->vxx);
+      query_rotate16_kernel<<<cdiv((long)M * H, 8), 256, 0, e->stream>>>(qraw, q_ld, H, dn, dr, L.freqs, s.rot_dims, s.rot_layout, sp.row_pos, q16, M);
+      CK(cudaGetLastError());
+      latent_gather_kernel<bf16><<<dim3(cdiv(fl->max_keys, 8), fl->n_reqs), 256, 0, e->stream>>>(static_cast<const bf16*>(L.pool), pg, fl->reqs, R + dr, cbuf);
+      CK(cudaGetLastError());
+      e->launches += 2;
+      TRY((product<bf16, bf16, bf16, 0>(e, cbuf, R + dr, 0, at<bf16>(e, L.uk_rows), R, 1, 0, knx, (long)H * dn, 0, fl->n_keys, H * dn, R, 1)));
+      TRY((product<bf16, bf16, bf16, 0>(e, cbuf, R + dr, 0, at<bf16>(e, L.uv), R, 1, 0, vxx, (long)H * dv, 0, fl->n_keys, H * dv, R, 1)));
+      const int dqp = (dn + dr + 15) & ~15, dvt = dv <= 64 ? 8 : 16;
+      const size_t smem = ((size_t)2 * 64 * (dqp + 8) + (size_t)8 * dvt * 72) * 2;
+      const dim3 grid(fl->n_tiles, H);
+      if (dvt == 8) {
+        auto kern = latent_flash_kernel<8>;
+        TRY(opt_in_smem(kern, smem));
+        kern<<<grid, 128, smem, e->stream>>>(q16, knx, cbuf, vxx, fl->tiles, H, dn, dr, dv, R, s.scale, s.window, gate, L.n_in, L.c_g, static_cast<bf16*>(e->oh));
+      } else {
+        auto kern = latent_flash_kernel<16>;
+        TRY(opt_in_smem(kern, smem));
+        kern<<<grid, 128, smem, e->stream>>>(q16, knx, cbuf, vxx, fl->tiles, H, dn, dr, dv, R, s.scale, s.window, gate, L.n_in, L.c_g, static_cast<bf16*>(e->oh));
+      }
+      CK(cudaGetLastError());
+      e->launches++;
+      e->flash_launches++;
+    }
+  }
+  // the output projection
   TRY((product<T, T, float, 0>(e, static_cast<T*>(e->oh), (long)H * dv, 0, at<T>(e, L.wo), (long)H * dv, 1, 0, e->y, D, 0, M, D, H * dv, 1)));
   return 0;
 }
@@ -633,7 +696,7 @@ int xotb200_lm_destroy(xotb200_lm* e) {
   free_state(e);
   for (auto& L : e->layers)
     if (L.freqs) cudaFree(L.freqs);
-  void* ptrs[] = {e->blob, e->d_stage, e->x, e->y, e->proj, e->qraw, e->qfull, e->wlog, e->oraw, e->logits, e->h, e->cqn, e->qn, e->olat, e->oh, e->act,
+  void* ptrs[] = {e->q16, e->cbuf, e->knx, e->vxx, e->blob, e->d_stage, e->x, e->y, e->proj, e->qraw, e->qfull, e->wlog, e->oraw, e->logits, e->h, e->cqn, e->qn, e->olat, e->oh, e->act,
                   e->th, e->hw, e->d_argmax, e->trace_buf};
   for (void* p : ptrs)
     if (p) cudaFree(p);
@@ -665,6 +728,36 @@ int xotb200_lm_load_tensor(xotb200_lm* e, const char* name, const void* bits, co
     return XOTB200_ESTRICT;
   }
   return upload_tensor(e, d, bits);
+}
+
+int xotb200_lm_init_synthetic(xotb200_lm* e, uint64_t seed) {
+  REQUIRE(e, "null engine");
+  CK(cudaSetDevice(e->device));
+  uint64_t k = 0;
+  for (auto& kv : e->dests) {
+    Dest& d = kv.second;
+    const std::string& name = kv.first;
+    const size_t n = (size_t)d.rows * d.cols, off = d.elem_off + (size_t)d.row_off * d.cols;
+    float mean = 0.f, dev = 1.0f / sqrtf((float)d.cols);
+    if (name.find("norm") != std::string::npos) { mean = 1.f; dev = 0.1f; }
+    else if (d.rows == 1) dev = 0.5f;                  // biases of the delta-rule gates
+    else if (name == "embed") dev = 1.f;
+    const int grid = (int)std::min<size_t>(8192, (n + 255) / 256);
+    if (e->esz == 2) fill_random_kernel<bf16><<<grid, 256, 0, e->stream>>>(at<bf16>(e, off), n, seed * 1000003ull + (++k), mean, dev);
+    else fill_random_kernel<float><<<grid, 256, 0, e->stream>>>(at<float>(e, off), n, seed * 1000003ull + (++k), mean, dev);
+    CK(cudaGetLastError());
+    e->launches++;
+    if (d.has2) {   // the row-major copy is the random one's transpose back: both layouts hold the same matrix
+      const int dh = d.rows / d.tr_heads;
+      if (e->esz == 2) untranspose_heads_kernel<bf16><<<grid, 256, 0, e->stream>>>(at<bf16>(e, off), at<bf16>(e, d.elem_off2), d.tr_heads, dh, d.cols);
+      else untranspose_heads_kernel<float><<<grid, 256, 0, e->stream>>>(at<float>(e, off), at<float>(e, d.elem_off2), d.tr_heads, dh, d.cols);
+      CK(cudaGetLastError());
+      e->launches++;
+    }
+    d.loaded = true;
+  }
+  CK(cudaStreamSynchronize(e->stream));
+  return 0;
 }
 
 int xotb200_lm_check_loaded(xotb200_lm* e) {
@@ -818,30 +911,18 @@ int xotb200_lm_step(xotb200_lm* e, int n_seq, const int32_t* slots, const int32_
   if (e->first)
     for (long m = 0; m < M; ++m) REQUIRE(tokens[m] >= 0 && tokens[m] < V, "token id %d outside the vocabulary of %d", tokens[m], V);
   TRY(ensure_scratch(e, (int)M, n_want));
-  // distinct work-item sizes of the attention layers
-  std::vector<int> qpis;
+  // ---- commit: pages and lengths; the step's index arrays are built in one host vector and copied once
+  const bool use_flash = e->esz == 2 && e->flash_on;
+  std::vector<int> qpis, windows;
   for (auto& L : e->layers)
     if (L.s.mixer == XOTB200_LM_MIX_LATENT_ATTN) {
       const int q = std::max(1, 32 / L.s.heads);
       if (std::find(qpis.begin(), qpis.end(), q) == qpis.end()) qpis.push_back(q);
+      if (use_flash && std::find(windows.begin(), windows.end(), L.s.window) == windows.end()) windows.push_back(L.s.window);
     }
-  size_t ints = 3 * (size_t)M + n_want + 4 * (size_t)n_seq;
-  for (int q : qpis)
-    for (int i = 0; i < n_seq; ++i) ints += 4 * (size_t)cdiv(counts[i], q);
-  if (ints > e->stage_cap) {
-    if (e->h_stage) cudaFreeHost(e->h_stage);
-    if (e->d_stage) cudaFree(e->d_stage);
-    e->h_stage = nullptr; e->d_stage = nullptr; e->stage_cap = 0;
-    const size_t cap = std::max<size_t>(ints * 2, 4096);
-    CK(cudaHostAlloc(&e->h_stage, cap * 4, cudaHostAllocDefault));
-    CK(cudaMalloc(&e->d_stage, cap * 4));
-    e->stage_cap = cap;
-  }
-  // ---- commit: pages, lengths, staging arrays
-  int* hs = e->h_stage;
-  int *h_tok = hs, *h_slot = hs + M, *h_pos = hs + 2 * M, *h_want = hs + 3 * M;
-  Item* h_seq = reinterpret_cast<Item*>(hs + 3 * M + n_want);
-  size_t off = 3 * (size_t)M + n_want + 4 * (size_t)n_seq;
+  std::vector<int>& st = e->stage_build;
+  st.assign(3 * (size_t)M + n_want, 0);
+  std::vector<Item> seqs(n_seq);
   StepPlan sp;
   sp.M = (int)M;
   sp.n_seq = n_seq;
@@ -858,31 +939,81 @@ int xotb200_lm_step(xotb200_lm* e, int n_seq, const int32_t* slots, const int32_
                          cudaMemcpyHostToDevice, e->stream));
     e->slot_pages[sl] = np1;
     e->slot_len[sl] = len1;
-    h_seq[i] = Item{row, counts[i], sl, len0};
+    seqs[i] = Item{row, counts[i], sl, len0};
     for (int t = 0; t < counts[i]; ++t, ++row) {
-      h_tok[row] = e->first ? tokens[row] : 0;
-      h_slot[row] = sl;
-      h_pos[row] = len0 + t;
+      st[row] = e->first ? tokens[row] : 0;
+      st[M + row] = sl;
+      st[2 * M + row] = len0 + t;
     }
   }
-  for (int w = 0; w < n_want; ++w) h_want[w] = want_rows[w];
+  for (int w = 0; w < n_want; ++w) st[3 * M + w] = want_rows[w];
+  auto push = [&](const void* p, size_t n_ints) { const size_t o = st.size(); const int* q = static_cast<const int*>(p); st.insert(st.end(), q, q + n_ints); return o; };
+  const size_t off_seqs = push(seqs.data(), 4 * (size_t)n_seq);
+  auto is_long = [&](int i) { return use_flash && counts[i] >= FLASH_MIN_ROWS; };
   std::map<int, std::pair<size_t, int>> item_off;
+  sp.any_short = false;
   for (int q : qpis) {
-    Item* it = reinterpret_cast<Item*>(hs + off);
-    int n = 0;
+    std::vector<Item> it;
     for (int i = 0; i < n_seq; ++i)
-      for (int t = 0; t < counts[i]; t += q) it[n++] = Item{h_seq[i].row0 + t, std::min(q, counts[i] - t), h_seq[i].slot, h_seq[i].pos0 + t};
-    item_off[q] = {off, n};
-    off += 4 * (size_t)n;
+      if (!is_long(i))
+        for (int t = 0; t < counts[i]; t += q) it.push_back(Item{seqs[i].row0 + t, std::min(q, counts[i] - t), seqs[i].slot, seqs[i].pos0 + t});
+    item_off[q] = {push(it.data(), 4 * it.size()), (int)it.size()};
+    if (!it.empty()) sp.any_short = true;
   }
+  struct FlashOff { size_t reqs, tiles; int n_reqs, n_tiles, n_keys, max_keys; };
+  std::map<int, FlashOff> flash_off;
+  size_t flash_keys = 0;
+  for (int w : windows) {
+    std::vector<GatherReq> gr;
+    std::vector<FlashTile> ft;
+    int kbase = 0, max_keys = 0;
+    for (int i = 0; i < n_seq; ++i)
+      if (is_long(i)) {
+        const int kfirst = w > 0 ? std::max(0, seqs[i].pos0 - w + 1) : 0;
+        const int nkeys = seqs[i].pos0 + counts[i] - kfirst;
+        gr.push_back(GatherReq{seqs[i].slot, kfirst, nkeys, kbase});
+        for (int t = 0; t < counts[i]; t += 64) ft.push_back(FlashTile{seqs[i].row0 + t, std::min(64, counts[i] - t), seqs[i].pos0 + t, kbase, kfirst});
+        kbase += nkeys;
+        max_keys = std::max(max_keys, nkeys);
+      }
+    if (gr.empty()) continue;
+    flash_off[w] = FlashOff{push(gr.data(), 4 * gr.size()), push(ft.data(), 5 * ft.size()), (int)gr.size(), (int)ft.size(), kbase, max_keys};
+    flash_keys = std::max(flash_keys, (size_t)kbase);
+  }
+  if (flash_keys > e->flash_keys_cap) {
+    const size_t cap = std::max<size_t>(flash_keys, 1024);
+    TRY(regrow(e->cbuf, cap * e->max_w * 2));
+    TRY(regrow(e->knx, cap * e->max_hdn * 2));
+    TRY(regrow(e->vxx, cap * e->max_oh * 2));
+    e->flash_keys_cap = cap;
+  }
+  const size_t off = st.size();
+  if (off > e->stage_cap) {
+    CK(cudaStreamSynchronize(e->stream));
+    if (e->h_stage) cudaFreeHost(e->h_stage);
+    if (e->d_stage) cudaFree(e->d_stage);
+    e->h_stage = nullptr; e->d_stage = nullptr; e->stage_cap = 0;
+    const size_t cap = std::max<size_t>(off * 2, 4096);
+    CK(cudaHostAlloc(&e->h_stage, cap * 4, cudaHostAllocDefault));
+    CK(cudaMalloc(&e->d_stage, cap * 4));
+    e->stage_cap = cap;
+  }
+  memcpy(e->h_stage, st.data(), off * 4);
   CK(cudaEventRecord(e->ev0, e->stream));
-  CK(cudaMemcpyAsync(e->d_stage, hs, off * 4, cudaMemcpyHostToDevice, e->stream));
+  CK(cudaMemcpyAsync(e->d_stage, e->h_stage, off * 4, cudaMemcpyHostToDevice, e->stream));
   sp.tokens = e->d_stage;
   sp.row_slot = e->d_stage + M;
   sp.row_pos = e->d_stage + 2 * M;
   sp.want = e->d_stage + 3 * M;
-  sp.seqs = reinterpret_cast<const Item*>(e->d_stage + 3 * M + n_want);
+  sp.seqs = reinterpret_cast<const Item*>(e->d_stage + off_seqs);
   for (auto& kv : item_off) sp.items[kv.first] = {reinterpret_cast<const Item*>(e->d_stage + kv.second.first), kv.second.second};
+  for (auto& kv : flash_off) {
+    StepPlan::Flash f;
+    f.reqs = reinterpret_cast<const GatherReq*>(e->d_stage + kv.second.reqs);
+    f.tiles = reinterpret_cast<const FlashTile*>(e->d_stage + kv.second.tiles);
+    f.n_reqs = kv.second.n_reqs; f.n_tiles = kv.second.n_tiles; f.n_keys = kv.second.n_keys; f.max_keys = kv.second.max_keys;
+    sp.flash[kv.first] = f;
+  }
   if (!e->first) CK(cudaMemcpyAsync(e->x, hidden_f32, (size_t)M * D * 4, cudaMemcpyHostToDevice, e->stream));
   {
     int rc = e->esz == 2 ? run_layers<bf16>(e, sp, n_want) : run_layers<float>(e, sp, n_want);
@@ -940,6 +1071,18 @@ int xotb200_lm_set_gemm_mode(xotb200_lm* e, int mode) {
 int xotb200_lm_kernel_launches(xotb200_lm* e, int64_t* count) {
   REQUIRE(e && count, "null argument");
   *count = e->launches;
+  return 0;
+}
+
+int xotb200_lm_set_attention_mode(xotb200_lm* e, int mode) {
+  REQUIRE(e && mode >= 0 && mode <= 1, "attention mode must be 0 or 1");
+  e->flash_on = mode == 0;
+  return 0;
+}
+
+int xotb200_lm_prompt_attention_launches(xotb200_lm* e, int64_t* count) {
+  REQUIRE(e && count, "null argument");
+  *count = e->flash_launches;
   return 0;
 }
 

@@ -518,6 +518,19 @@ __global__ void store_rows_kernel(const bf16* __restrict__ src, T* __restrict__ 
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
     stf(dst + i, __bfloat162float(src[i]));
 }
+// synthetic weights: element i = mean + dev * (uniform in [-sqrt 3, sqrt 3)) from a counter hash — for benchmarks and smoke runs
+template <typename T>
+__global__ void fill_random_kernel(T* __restrict__ dst, size_t n, uint64_t seed, float mean, float dev) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    uint64_t z = (i + 1) * 0x9E3779B97F4A7C15ull + seed;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    z ^= z >> 31;
+    const float u = (float)(z >> 40) * (1.0f / 16777216.0f);          // [0, 1)
+    stf(dst + i, mean + dev * 3.4641016f * (u - 0.5f));
+  }
+}
+
 // src [heads * d, cols] (row-major, bf16 bits) -> dst [heads][cols][d]: each head's block transposed
 template <typename T>
 __global__ void store_heads_transposed_kernel(const bf16* __restrict__ src, T* __restrict__ dst, int heads, int d, int cols) {
@@ -528,10 +541,248 @@ __global__ void store_heads_transposed_kernel(const bf16* __restrict__ src, T* _
     stf(dst + i, __bfloat162float(src[(h * d + k) * cols + c]));
   }
 }
+// the inverse: src [heads][cols][d] -> dst [heads * d, cols]
+template <typename T>
+__global__ void untranspose_heads_kernel(const T* __restrict__ src, T* __restrict__ dst, int heads, int d, int cols) {
+  const size_t n = (size_t)heads * d * cols;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t h = i / ((size_t)d * cols), r = i % ((size_t)d * cols);
+    const size_t c = r / d, k = r % d;
+    dst[(h * d + k) * cols + c] = src[i];
+  }
+}
 __global__ void copy_rows_f32_kernel(const float* __restrict__ src, float* __restrict__ dst, int ld_src, int ld_dst, int n, int M) {
   const size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
   if (i >= (size_t)M * n) return;
   dst[(i / n) * ld_dst + i % n] = src[(i / n) * ld_src + i % n];
+}
+
+
+// ===========================================================================================================================
+// Prompt attention on the tensor cores (bf16 serving path; requests that bring FLASH_MIN_ROWS rows or more).
+//
+// For many query rows the EXPANDED form is cheaper than the absorbed one: the visible cached rows of the request are gathered
+// from the paged pool into a contiguous buffer (latent_gather_kernel), expanded once per step by two tensor-core products into
+// per-head unrotated keys kn = c W_uk^T and values v = c W_uv^T, and latent_flash_kernel then runs a streaming-softmax attention
+// per (64-row tile, head) with mma.sync.m16n8k16 (bf16 operands, fp32 accumulators): scores = [q_unrot | q_rot] . [kn | kr],
+// fp32 scale / mask / running max and sum, and the weights enter the value product as a bf16 PAIR (high part + remainder, two
+// MMAs) so that they keep 16 mantissa bits instead of 8.  Key range as in the absorbed kernel: j <= i and (window == 0 or
+// i - j < window).  Output: o[m, h * dv + :] (bf16), times sigmoid(gate[m, h]) when the mixer is gated.
+// ===========================================================================================================================
+constexpr int FLASH_MIN_ROWS = 16;
+
+struct GatherReq {
+  int slot;      // request
+  int kfirst;    // first cached position that any row of the step can see
+  int nkeys;     // positions kfirst .. kfirst + nkeys - 1 (up to the request's last row of this step)
+  int kbase;     // index of position kfirst in the gathered buffers
+};
+
+struct FlashTile {
+  int row0;      // first packed row
+  int n_rows;    // <= 64 consecutive rows of one request
+  int pos0;      // position of row0
+  int kbase;     // as in GatherReq
+  int kfirst;
+};
+
+template <typename T>
+__global__ void latent_gather_kernel(const T* __restrict__ pool, Paging pg, const GatherReq* __restrict__ reqs, int W, T* __restrict__ cbuf) {
+  const GatherReq rq = reqs[blockIdx.y];
+  const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (i >= rq.nkeys) return;
+  const T* src = pool + pg.row(rq.slot, rq.kfirst + i) * (size_t)W;
+  T* dst = cbuf + (size_t)(rq.kbase + i) * W;
+  for (int d = lane; d < W; d += 32) dst[d] = src[d];
+}
+
+// Query in 16 bits for the expanded form: q16[m, h, 0:dn] = unrotated part, q16[m, h, dn:dn+dr] = rotated part turned by the position
+__global__ void query_rotate16_kernel(const float* __restrict__ qraw, int ld, int H, int dn, int dr, const float* __restrict__ freqs, int rot_dims,
+                                      int layout, const int* __restrict__ row_pos, bf16* __restrict__ q16, int M) {
+  const int idx = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (idx >= M * H) return;
+  const int m = idx / H, h = idx % H;
+  const float* q = qraw + (size_t)m * ld + (size_t)h * (dn + dr);
+  bf16* out = q16 + ((size_t)m * H + h) * (dn + dr);
+  for (int d = lane; d < dn; d += 32) out[d] = __float2bfloat16_rn(q[d]);
+  const float p = (float)row_pos[m];
+  const float* qr = q + dn;
+  for (int i = lane; i < rot_dims / 2; i += 32) {
+    int a, b;
+    rot_pair_index(i, rot_dims, layout, a, b);
+    const float ang = p * freqs[i], c = cosf(ang), sn = sinf(ang);
+    const float u = qr[a], v = qr[b];
+    out[dn + a] = __float2bfloat16_rn(u * c - v * sn);
+    out[dn + b] = __float2bfloat16_rn(v * c + u * sn);
+  }
+  for (int d = rot_dims + lane; d < dr; d += 32) out[dn + d] = __float2bfloat16_rn(qr[d]);
+}
+
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&p);
+}
+// 8 consecutive bf16 from p (n_valid of them exist, the rest read as zero) -> dst (16-byte aligned shared memory)
+__device__ __forceinline__ void stage8(bf16* dst, const bf16* p, int n_valid, bool vec) {
+  if (n_valid >= 8 && vec) {
+    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(p);
+  } else {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) dst[e] = e < n_valid ? p[e] : __float2bfloat16_rn(0.f);
+  }
+}
+
+template <int DVT>   // value columns held per warp row: DVT tiles of 8 (dv <= 8 * DVT)
+__global__ void __launch_bounds__(128)
+latent_flash_kernel(const bf16* __restrict__ q16, const bf16* __restrict__ kn, const bf16* __restrict__ cbuf, const bf16* __restrict__ vx,
+                    const FlashTile* __restrict__ tiles, int H, int dn, int dr, int dv, int R, float scale, int window, const float* __restrict__ gate,
+                    int gate_ld, int gate_col0, bf16* __restrict__ out) {
+  extern __shared__ __align__(16) uint8_t fsm[];
+  const FlashTile tl = tiles[blockIdx.x];
+  const int h = blockIdx.y;
+  const int DQ = dn + dr, DQP = (DQ + 15) & ~15, QS = DQP + 8;       // padded row length and row stride (elements) of the Q / K tiles
+  constexpr int VS = 64 + 8;                                         // row stride of the transposed V tile [value column][key]
+  bf16* Qs = reinterpret_cast<bf16*>(fsm);
+  bf16* Ks = Qs + 64 * QS;
+  bf16* Vt = Ks + 64 * QS;                                           // [8 * DVT][VS]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const bool vq = (DQ % 8 == 0), vk = (dn % 8 == 0) && ((H * dn) % 8 == 0), vr = (dr % 8 == 0) && (R % 8 == 0) && dn % 8 == 0,
+             vv = (dv % 8 == 0);
+
+  // ---- Q tile (rows beyond n_rows and the padding read as zero)
+  for (int e = threadIdx.x; e < 64 * (DQP / 8); e += 128) {
+    const int r = e / (DQP / 8), c = (e % (DQP / 8)) * 8;
+    const int nv = r < tl.n_rows ? max(0, min(8, DQ - c)) : 0;
+    stage8(Qs + r * QS + c, q16 + ((size_t)(tl.row0 + r) * H + h) * DQ + c, nv, vq);
+  }
+  float o[DVT][4];
+#pragma unroll
+  for (int i = 0; i < DVT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float mx[2] = {-INFINITY, -INFINITY}, den[2] = {0.f, 0.f};
+  const int pos_lo = tl.pos0 + warp * 16 + g, pos_hi = pos_lo + 8;   // positions of this thread's two rows
+  const int last = tl.pos0 + tl.n_rows - 1;
+  const int first = window > 0 ? max(0, tl.pos0 - window + 1) : 0;
+
+  for (int j0 = first; j0 <= last; j0 += 64) {
+    __syncthreads();
+    // ---- K tile: [kn(h) | kr] per key, V tile transposed
+    for (int e = threadIdx.x; e < 64 * (DQP / 8); e += 128) {
+      const int r = e / (DQP / 8), c = (e % (DQP / 8)) * 8, j = j0 + r;
+      bf16* dst = Ks + r * QS + c;
+      const size_t idx = (size_t)(tl.kbase + (j - tl.kfirst));
+      if (j > last || c >= DQ) stage8(dst, kn, 0, false);
+      else if (c + 8 <= dn) stage8(dst, kn + idx * ((size_t)H * dn) + (size_t)h * dn + c, 8, vk);
+      else if (c >= dn) stage8(dst, cbuf + idx * (size_t)(R + dr) + R + (c - dn), min(8, DQ - c), vr);
+      else {   // a chunk that straddles the two sources (dn not a multiple of 8)
+#pragma unroll
+        for (int x = 0; x < 8; ++x) {
+          const int d = c + x;
+          dst[x] = d < dn ? kn[idx * ((size_t)H * dn) + (size_t)h * dn + d] : d < DQ ? cbuf[idx * (size_t)(R + dr) + R + (d - dn)] : __float2bfloat16_rn(0.f);
+        }
+      }
+    }
+    for (int e = threadIdx.x; e < 64 * DVT; e += 128) {
+      const int r = e / DVT, c = (e % DVT) * 8, j = j0 + r;
+      __align__(16) bf16 tmp[8];
+      const int nv = j <= last ? max(0, min(8, dv - c)) : 0;
+      stage8(tmp, vx + (size_t)(tl.kbase + (j - tl.kfirst)) * ((size_t)H * dv) + (size_t)h * dv + c, nv, vv);
+#pragma unroll
+      for (int x = 0; x < 8; ++x) Vt[(c + x) * VS + r] = tmp[x];
+    }
+    __syncthreads();
+    // ---- scores of this warp's 16 rows against the 64 keys
+    float s[8][4];
+#pragma unroll
+    for (int n = 0; n < 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+    const bf16* qa = Qs + (warp * 16 + g) * QS + 2 * t;
+    for (int k0 = 0; k0 < DQP; k0 += 16) {
+      const uint32_t a0 = *reinterpret_cast<const uint32_t*>(qa + k0), a1 = *reinterpret_cast<const uint32_t*>(qa + 8 * QS + k0);
+      const uint32_t a2 = *reinterpret_cast<const uint32_t*>(qa + k0 + 8), a3 = *reinterpret_cast<const uint32_t*>(qa + 8 * QS + k0 + 8);
+#pragma unroll
+      for (int n = 0; n < 8; ++n) {
+        const bf16* kb = Ks + (n * 8 + g) * QS + k0 + 2 * t;
+        mma_bf16_16816(s[n], a0, a1, a2, a3, *reinterpret_cast<const uint32_t*>(kb), *reinterpret_cast<const uint32_t*>(kb + 8));
+      }
+    }
+    // ---- scale, mask, running max
+    float tmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int n = 0; n < 8; ++n)
+#pragma unroll
+      for (int x = 0; x < 4; ++x) {
+        const int j = j0 + n * 8 + 2 * t + (x & 1), pos = (x < 2) ? pos_lo : pos_hi;
+        const bool vis = j <= pos && j <= last && (window == 0 || pos - j < window);
+        s[n][x] = vis ? s[n][x] * scale : -INFINITY;
+        tmax[x >> 1] = fmaxf(tmax[x >> 1], s[n][x]);
+      }
+    float corr[2], nmx[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 1));
+      tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 2));
+      nmx[r] = fmaxf(mx[r], tmax[r]);
+      corr[r] = (mx[r] == -INFINITY) ? 0.f : expf(mx[r] - nmx[r]);
+      mx[r] = nmx[r];
+    }
+    float psum[2] = {0.f, 0.f};
+#pragma unroll
+    for (int n = 0; n < 8; ++n)
+#pragma unroll
+      for (int x = 0; x < 4; ++x) {
+        const float p = (s[n][x] == -INFINITY) ? 0.f : expf(s[n][x] - nmx[x >> 1]);
+        s[n][x] = p;
+        psum[x >> 1] += p;
+      }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      psum[r] += __shfl_xor_sync(0xffffffffu, psum[r], 1);
+      psum[r] += __shfl_xor_sync(0xffffffffu, psum[r], 2);
+      den[r] = den[r] * corr[r] + psum[r];
+    }
+#pragma unroll
+    for (int i = 0; i < DVT; ++i) { o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1]; }
+    // ---- o += P V with P as (high, remainder) bf16 pairs
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {
+      uint32_t ah[4], al[4];
+#pragma unroll
+      for (int x = 0; x < 4; ++x) {
+        const float p0 = s[2 * kk + (x >> 1)][(x & 1) * 2], p1 = s[2 * kk + (x >> 1)][(x & 1) * 2 + 1];
+        const float h0 = __bfloat162float(__float2bfloat16_rn(p0)), h1 = __bfloat162float(__float2bfloat16_rn(p1));
+        ah[x] = pack_bf16x2(h0, h1);
+        al[x] = pack_bf16x2(p0 - h0, p1 - h1);
+      }
+#pragma unroll
+      for (int i = 0; i < DVT; ++i) {
+        const bf16* vb = Vt + (i * 8 + g) * VS + kk * 16 + 2 * t;
+        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(vb), b1 = *reinterpret_cast<const uint32_t*>(vb + 8);
+        mma_bf16_16816(o[i], ah[0], ah[1], ah[2], ah[3], b0, b1);
+        mma_bf16_16816(o[i], al[0], al[1], al[2], al[3], b0, b1);
+      }
+    }
+  }
+  // ---- normalise, gate, store
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int qi = warp * 16 + g + r * 8;
+    if (qi >= tl.n_rows) continue;
+    const int m = tl.row0 + qi;
+    float sc = 1.0f / den[r];
+    if (gate) sc *= sigmoidf_(gate[(size_t)m * gate_ld + gate_col0 + h]);
+    bf16* dst = out + (size_t)m * ((size_t)H * dv) + (size_t)h * dv;
+#pragma unroll
+    for (int i = 0; i < DVT; ++i)
+#pragma unroll
+      for (int x = 0; x < 2; ++x) {
+        const int c = i * 8 + 2 * t + x;
+        if (c < dv) dst[c] = __float2bfloat16_rn(o[i][r * 2 + x] * sc);
+      }
+  }
 }
 
 }  // namespace xl

@@ -177,6 +177,10 @@ class LayeredShard:
     shp = (C.c_int64 * a.ndim)(*a.shape)
     return check_lm(self.lib.xotb200_lm_load_tensor(self.h, name.encode(), a.ctypes.data_as(C.c_void_p), shp, a.ndim)) == 0
 
+  def init_synthetic(self, seed: int = 1234):
+    """random weights made on the device (after set_shard): benchmarks and smoke runs"""
+    check_lm(self.lib.xotb200_lm_init_synthetic(self.h, int(seed)))
+
   def check_loaded(self):
     check_lm(self.lib.xotb200_lm_check_loaded(self.h))
 
@@ -279,6 +283,14 @@ class LayeredShard:
   def kernel_launches(self) -> int:
     v = C.c_int64()
     check_lm(self.lib.xotb200_lm_kernel_launches(self.h, C.byref(v)))
+    return int(v.value)
+
+  def set_attention_mode(self, mode: int):
+    check_lm(self.lib.xotb200_lm_set_attention_mode(self.h, int(mode)))
+
+  def prompt_attention_launches(self) -> int:
+    v = C.c_int64()
+    check_lm(self.lib.xotb200_lm_prompt_attention_launches(self.h, C.byref(v)))
     return int(v.value)
 
   def tensor_core_launches(self) -> int:
