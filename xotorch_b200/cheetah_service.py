@@ -70,13 +70,14 @@ class CheetahService:
     eng = self.engines.get(key)
     if eng is None:
       cfg = json.loads((Path(key[0]) / "config.json").read_text())
-      if int(hdr["layer_total"]) != cfg["num_hidden_layers"]:
-        raise ValueError(f"layer_total {hdr['layer_total']} but the model has {cfg['num_hidden_layers']} layers")
+      from xotorch_b200.models import make_native, model_summary
+      depth = model_summary(cfg)["n_layers"]
+      if int(hdr["layer_total"]) != depth:
+        raise ValueError(f"layer_total {hdr['layer_total']} but the model has {depth} layers")
       if self._factory is not None:
         eng = self._factory(cfg, self.device)
       else:
-        from xotorch_b200.native import NativeShard            # raises if libxotb200.so is missing: no CPU fallback
-        eng = NativeShard(cfg, self.device)
+        eng = make_native(cfg, self.device)                    # the family's native engine; raises if its library is missing
       eng.load_dir(key[0], key[1], key[2])
       eng._cheetah_cfg = cfg
       self.engines[key] = eng
@@ -108,7 +109,8 @@ class CheetahService:
       pos0 = int(pos.reshape(-1)[0])
       data = ids.reshape(1, n).astype(np.int32)
     if pos0 == 0:                                     # a new request on this shard: KV of prompt + 1024 like the reference
-      need = min(n + 1024, int(cfg["max_position_embeddings"]))
+      from xotorch_b200.models import model_summary
+      need = min(n + 1024, int(model_summary(cfg)["max_positions"]))
       eng.begin_request(need)
     out = eng.forward(data, pos0)
     self.sessions[skey] = pos0 + n

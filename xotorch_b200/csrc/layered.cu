@@ -112,10 +112,12 @@ struct xotb200_lm {
   size_t stage_cap = 0;
   // scratch (rows capacity m_cap)
   int m_cap = 0, want_cap = 0;
-  float *x = nullptr, *y = nullptr, *proj = nullptr, *qraw = nullptr, *qfull = nullptr, *wlog = nullptr, *oraw = nullptr, *logits = nullptr;
+  float *x = nullptr, *y = nullptr, *proj = nullptr, *qraw = nullptr, *qfull = nullptr, *wlog = nullptr, *oraw = nullptr, *du = nullptr, *dau = nullptr, *logits = nullptr;
   void *h = nullptr, *cqn = nullptr, *qn = nullptr, *olat = nullptr, *oh = nullptr, *act = nullptr, *th = nullptr, *hw = nullptr;
   void *q16 = nullptr, *cbuf = nullptr, *knx = nullptr, *vxx = nullptr;   // expanded prompt attention (bf16)
   size_t flash_keys_cap = 0;
+  float* part = nullptr;                               // key-run partial results of the absorbed attention kernel
+  size_t part_cap = 0;
   int max_w = 0;                                       // widest cached row (kv_rank + rot_dim)
   int* d_argmax = nullptr;
   float* h_out = nullptr;                              // pinned staging for results
@@ -379,6 +381,8 @@ static int ensure_scratch(xotb200_lm* e, int M, int n_want) {
     TRY(regrow(e->qfull, m * e->max_qfull * 4));
     TRY(regrow(e->wlog, m * e->max_hd * 4));
     TRY(regrow(e->oraw, m * e->max_hd * 4));
+    TRY(regrow(e->du, m * e->max_hd * 4));
+    TRY(regrow(e->dau, m * e->max_hd * 4));
     TRY(regrow(e->h, m * D * z));
     TRY(regrow(e->cqn, m * e->max_qr * z));
     TRY(regrow(e->qn, m * e->max_hdn * z));
@@ -427,6 +431,7 @@ struct StepPlan {
     int n_reqs = 0, n_tiles = 0, n_keys = 0, max_keys = 0;
   };
   std::map<int, Flash> flash;
+  int max_len = 0;                                     // longest request after this step (bounds every key range)
   bool any_short = true;                               // some request goes through the absorbed kernel
 };
 
@@ -473,15 +478,25 @@ static int attention_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
     const int qpi = std::max(1, 32 / H);
     const auto& it = sp.items.at(qpi);
     if (it.second > 0) {
-      const int pairs = qpi * H, nw = std::min(32, pairs);
+      const int pairs = qpi * H, nw = std::min(R > 256 ? 16 : 32, pairs);   // the widest accumulator variant needs 70 registers: 16 warps at most
       const size_t smem = ((size_t)32 * ((R + dr) | 1) + (size_t)nw * (R + dr)) * 4;
-      const dim3 grid(it.second, cdiv(pairs, nw));
+      // few work items (decoding): cut the keys into runs so that the GPU is filled; each run at least 64 keys
+      const int span = s.window > 0 ? std::min(sp.max_len, s.window + qpi) : sp.max_len;
+      int splits = 1;
+      if (it.second * cdiv(pairs, nw) < e->sm_count) splits = std::max(1, std::min(cdiv(span, 64), cdiv(2 * e->sm_count, it.second * cdiv(pairs, nw))));
+      const int chunk = cdiv(cdiv(span, splits), 32) * 32;
+      splits = cdiv(span, chunk);
+      if (splits > 1) {
+        const size_t need = (size_t)M * H * splits * (2 + R);
+        if (need > e->part_cap) { TRY(regrow(e->part, need * 4)); e->part_cap = need; }
+      }
+      const dim3 grid(it.second, cdiv(pairs, nw), splits);
 #define LAUNCH_ATTN(NACC)                                                                                                                       \
   do {                                                                                                                                          \
     auto kern = latent_attention_kernel<T, NACC>;                                                                                               \
     TRY(opt_in_smem(kern, smem));                                                                                                               \
     kern<<<grid, nw * 32, smem, e->stream>>>(e->qfull, static_cast<const T*>(L.pool), pg, it.first, H, R, dr, s.scale, s.window, gate, L.n_in, \
-                                             L.c_g, static_cast<T*>(e->olat));                                                                  \
+                                             L.c_g, static_cast<T*>(e->olat), chunk, e->part);                                                  \
   } while (0)
       if (R <= 64) LAUNCH_ATTN(2);
       else if (R <= 128) LAUNCH_ATTN(4);
@@ -490,6 +505,11 @@ static int attention_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
 #undef LAUNCH_ATTN
       CK(cudaGetLastError());
       e->launches++;
+      if (splits > 1) {
+        latent_attention_combine_kernel<T><<<it.second, 256, 0, e->stream>>>(e->part, it.first, H, R, splits, gate, L.n_in, L.c_g, static_cast<T*>(e->olat));
+        CK(cudaGetLastError());
+        e->launches++;
+      }
     }
     // value expansion per head
     TRY((product<T, T, T, 0>(e, static_cast<T*>(e->olat), (long)H * R, R, at<T>(e, L.uv), R, 1, (long)dv * R, static_cast<T*>(e->oh), (long)H * dv, dv, M, dv,
@@ -528,14 +548,13 @@ static int attention_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
   return 0;
 }
 
-template <typename T, int KPT, int P>
+template <int KPT, int P>
 static int launch_delta(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
   const xotb200_lm_layer& s = L.s;
   constexpr int CPW = 32 / P, WARPS = 4;
   const dim3 grid(sp.n_seq * s.heads, cdiv(s.vdim, WARPS * CPW));
-  delta_rule_kernel<T, KPT, P><<<grid, WARPS * 32, (size_t)8 * s.vdim * 4, e->stream>>>(
-      e->proj, L.n_in, L.c_r, L.c_k, L.c_v, L.c_a, e->wlog, at<T>(e, L.w0), at<T>(e, L.a_b), sp.seqs, s.heads, s.dim, s.vdim, e->state + L.state_off,
-      e->state_floats, e->oraw);
+  delta_rule_kernel<KPT, P><<<grid, WARPS * 32, 0, e->stream>>>(e->proj, L.n_in, L.c_r, L.c_k, L.c_v, e->wlog, e->du, e->dau, sp.seqs, s.heads, s.dim, s.vdim,
+                                                                e->state + L.state_off, e->state_floats, e->oraw);
   CK(cudaGetLastError());
   e->launches++;
   return 0;
@@ -551,11 +570,15 @@ static int delta_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
   CK(cudaGetLastError());
   e->launches++;
   TRY((product<T, T, float, 0>(e, static_cast<T*>(e->th), s.low_rank, 0, at<T>(e, L.w2), s.low_rank, 1, 0, e->wlog, HD, 0, M, HD, s.low_rank, 1)));
-  if (s.dim <= 16) TRY((launch_delta<T, 16, 1>(e, L, sp)));
-  else if (s.dim <= 32) TRY((launch_delta<T, 16, 2>(e, L, sp)));
-  else if (s.dim <= 64) TRY((launch_delta<T, 16, 4>(e, L, sp)));
-  else if (s.dim <= 128) TRY((launch_delta<T, 16, 8>(e, L, sp)));
-  else TRY((launch_delta<T, 32, 8>(e, L, sp)));
+  delta_prepare_kernel<T><<<cdiv((long)M * s.heads, 8), 256, 0, e->stream>>>(e->proj, L.n_in, L.c_k, L.c_a, e->wlog, at<T>(e, L.w0), at<T>(e, L.a_b), e->du, e->dau,
+                                                                              s.heads, s.dim, M);
+  CK(cudaGetLastError());
+  e->launches++;
+  if (s.dim <= 16) TRY((launch_delta<16, 1>(e, L, sp)));
+  else if (s.dim <= 32) TRY((launch_delta<16, 2>(e, L, sp)));
+  else if (s.dim <= 64) TRY((launch_delta<16, 4>(e, L, sp)));
+  else if (s.dim <= 128) TRY((launch_delta<16, 8>(e, L, sp)));
+  else TRY((launch_delta<32, 8>(e, L, sp)));
   head_norm_gate_kernel<T><<<cdiv((long)M * s.heads, 8), 256, 0, e->stream>>>(e->oraw, at<T>(e, L.onorm), e->proj, L.n_in, L.c_g, static_cast<T*>(e->oh), s.heads,
                                                                                s.vdim, e->cfg.norm_eps, M);
   CK(cudaGetLastError());
@@ -696,7 +719,7 @@ int xotb200_lm_destroy(xotb200_lm* e) {
   free_state(e);
   for (auto& L : e->layers)
     if (L.freqs) cudaFree(L.freqs);
-  void* ptrs[] = {e->q16, e->cbuf, e->knx, e->vxx, e->blob, e->d_stage, e->x, e->y, e->proj, e->qraw, e->qfull, e->wlog, e->oraw, e->logits, e->h, e->cqn, e->qn, e->olat, e->oh, e->act,
+  void* ptrs[] = {e->du, e->dau, e->part, e->q16, e->cbuf, e->knx, e->vxx, e->blob, e->d_stage, e->x, e->y, e->proj, e->qraw, e->qfull, e->wlog, e->oraw, e->logits, e->h, e->cqn, e->qn, e->olat, e->oh, e->act,
                   e->th, e->hw, e->d_argmax, e->trace_buf};
   for (void* p : ptrs)
     if (p) cudaFree(p);
@@ -940,6 +963,7 @@ int xotb200_lm_step(xotb200_lm* e, int n_seq, const int32_t* slots, const int32_
     e->slot_pages[sl] = np1;
     e->slot_len[sl] = len1;
     seqs[i] = Item{row, counts[i], sl, len0};
+    sp.max_len = std::max(sp.max_len, len1);
     for (int t = 0; t < counts[i]; ++t, ++row) {
       st[row] = e->first ? tokens[row] : 0;
       st[M + row] = sl;

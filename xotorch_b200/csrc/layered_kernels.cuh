@@ -195,10 +195,14 @@ struct Item {
   int pos0;     // position of row0
 };
 
+// Key splits: with gridDim.z > 1 the keys of an item are cut into gridDim.z runs of `chunk` keys (a multiple of 32); CTA z handles
+// run z and parks its unnormalised result {running max, sum, accumulator[R]} in `part` ([M * H][gridDim.z][2 + R] fp32), and
+// latent_attention_combine_kernel merges the runs.  That is what keeps a single decoded row over a long context from running on
+// one SM.  With gridDim.z == 1 the kernel normalises, gates and stores itself.
 template <typename T, int NACC>
 __global__ void latent_attention_kernel(const float* __restrict__ qfull, const T* __restrict__ pool, Paging pg, const Item* __restrict__ items,
                                         int H, int R, int dr, float scale, int window, const float* __restrict__ gate, int gate_ld,
-                                        int gate_col0, T* __restrict__ olat) {
+                                        int gate_col0, T* __restrict__ olat, int chunk, float* __restrict__ part) {
   extern __shared__ float smem[];
   const Item it = items[blockIdx.x];
   const int W = R + dr, WS = W | 1;                 // odd row stride: lane j reading row j is conflict-free
@@ -214,23 +218,33 @@ __global__ void latent_attention_kernel(const float* __restrict__ qfull, const T
     const float* src = qfull + ((size_t)m * H + h) * W;
     for (int d = lane; d < W; d += 32) q[d] = src[d];
   }
-  const int last = it.pos0 + it.n_rows - 1;
-  const int first = window > 0 ? max(0, it.pos0 - window + 1) : 0;
+  int last = it.pos0 + it.n_rows - 1;
+  int first = window > 0 ? max(0, it.pos0 - window + 1) : 0;
+  if (gridDim.z > 1) {
+    first += blockIdx.z * chunk;
+    last = min(last, first + chunk - 1);
+  }
   float acc[NACC];
 #pragma unroll
   for (int a = 0; a < NACC; ++a) acc[a] = 0.f;
   float mx = -INFINITY, den = 0.f;
   for (int j0 = first; j0 <= last; j0 += 32) {
     __syncthreads();
-    // stage 32 cached rows (fp32) — rows past `last` are zero-filled
-    for (int e = threadIdx.x; e < 32 * W; e += blockDim.x) {
-      const int jr = e / W, d = e % W, j = j0 + jr;
-      ktile[jr * WS + d] = j <= last ? ldf(pool + pg.row(it.slot, j) * (size_t)W + d) : 0.f;
+    // stage 32 cached rows (fp32), one warp per row — rows past `last` are zero-filled
+    for (int jr = warp; jr < 32; jr += nw) {
+      const int j = j0 + jr;
+      float* dst = ktile + jr * WS;
+      if (j <= last) {
+        const T* src = pool + pg.row(it.slot, j) * (size_t)W;
+        for (int d = lane; d < W; d += 32) dst[d] = ldf(src + d);
+      } else {
+        for (int d = lane; d < W; d += 32) dst[d] = 0.f;
+      }
     }
     __syncthreads();
     if (!active) continue;
     const int j = j0 + lane;
-    const bool vis = j <= pos && (window == 0 || pos - j < window);
+    const bool vis = j <= pos && j <= last && (window == 0 || pos - j < window);
     float s = 0.f;
     const float* kr = ktile + lane * WS;
     for (int d = 0; d < W; ++d) s = fmaf(q[d], kr[d], s);
@@ -256,6 +270,16 @@ __global__ void latent_attention_kernel(const float* __restrict__ qfull, const T
     }
   }
   if (!active) return;
+  if (gridDim.z > 1) {
+    float* dst = part + (((size_t)m * H + h) * gridDim.z + blockIdx.z) * (size_t)(2 + R);
+    if (lane == 0) { dst[0] = mx; dst[1] = den; }
+#pragma unroll
+    for (int a = 0; a < NACC; ++a) {
+      const int d = a * 32 + lane;
+      if (d < R) dst[2 + d] = acc[a];
+    }
+    return;
+  }
   float g = 1.0f / den;
   if (gate) g *= sigmoidf_(gate[(size_t)m * gate_ld + gate_col0 + h]);
   T* out = olat + ((size_t)m * H + h) * R;
@@ -263,6 +287,35 @@ __global__ void latent_attention_kernel(const float* __restrict__ qfull, const T
   for (int a = 0; a < NACC; ++a) {
     const int d = a * 32 + lane;
     if (d < R) stf(out + d, acc[a] * g);
+  }
+}
+
+// merges the key runs of latent_attention_kernel: one warp per (row, head) pair of the listed items
+template <typename T>
+__global__ void latent_attention_combine_kernel(const float* __restrict__ part, const Item* __restrict__ items, int H, int R, int splits,
+                                                const float* __restrict__ gate, int gate_ld, int gate_col0, T* __restrict__ olat) {
+  const Item it = items[blockIdx.x];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  for (int pair = warp; pair < it.n_rows * H; pair += nw) {
+    const int m = it.row0 + pair / H, h = pair % H;
+    const float* src = part + ((size_t)m * H + h) * splits * (size_t)(2 + R);
+    float mx = -INFINITY;
+    for (int z = 0; z < splits; ++z) mx = fmaxf(mx, src[(size_t)z * (2 + R)]);
+    float den = 0.f;
+    for (int z = 0; z < splits; ++z) {
+      const float mz = src[(size_t)z * (2 + R)];
+      if (mz != -INFINITY) den += src[(size_t)z * (2 + R) + 1] * expf(mz - mx);
+    }
+    float g = 1.0f / den;
+    if (gate) g *= sigmoidf_(gate[(size_t)m * gate_ld + gate_col0 + h]);
+    for (int d = lane; d < R; d += 32) {
+      float a = 0.f;
+      for (int z = 0; z < splits; ++z) {
+        const float mz = src[(size_t)z * (2 + R)];
+        if (mz != -INFINITY) a += src[(size_t)z * (2 + R) + 2 + d] * expf(mz - mx);
+      }
+      stf(olat + ((size_t)m * H + h) * R + d, a * g);
+    }
   }
 }
 
@@ -277,14 +330,40 @@ __global__ void latent_attention_kernel(const float* __restrict__ qfull, const T
 //   proj: fp32 [M, ld] projection output with the r / k / v / a blocks (H * d columns each) at the given column offsets;
 //   wlog: fp32 [M, H * dk] decay logits (low-rank branch output), to which w_bias is added;   o_raw: fp32 [M, H * dv].
 // ---------------------------------------------------------------------------------------------------------------------------
-template <typename T, int KPT, int P>
-__global__ void delta_rule_kernel(const float* __restrict__ proj, int ld, int col_r, int col_k, int col_v, int col_a, const float* __restrict__ wlog,
-                                  const T* __restrict__ w_bias, const T* __restrict__ a_bias, const Item* __restrict__ seqs, int H, int dk,
+// The per-token vectors are made for all rows at once by delta_prepare_kernel (one warp per (row, head)): in place w <- decay
+// (wlog), and u, a * u into two fp32 buffers.  delta_rule_kernel then only carries the recurrence: the six vectors of 16 tokens
+// at a time (fewer for wide heads) come into shared memory with cp.async, double-buffered, while the previous 16 tokens are being applied.
+template <typename T>
+__global__ void delta_prepare_kernel(const float* __restrict__ proj, int ld, int col_k, int col_a, float* __restrict__ wlog, const T* __restrict__ w_bias,
+                                     const T* __restrict__ a_bias, float* __restrict__ u_out, float* __restrict__ au_out, int H, int dk, int M) {
+  const int idx = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (idx >= M * H) return;
+  const size_t m = idx / H;
+  const int h = idx % H;
+  const float* pr = proj + m * ld;
+  float ss = 0.f;
+  for (int i = lane; i < dk; i += 32) { const float kv = pr[col_k + h * dk + i]; ss = fmaf(kv, kv, ss); }
+  const float inv = 1.0f / sqrtf(warp_sum(ss) + 1e-6f);
+  for (int i = lane; i < dk; i += 32) {
+    const size_t o = m * (size_t)(H * dk) + h * dk + i;
+    const float u = pr[col_k + h * dk + i] * inv;
+    u_out[o] = u;
+    au_out[o] = sigmoidf_(pr[col_a + h * dk + i] + ldf(a_bias + h * dk + i)) * u;
+    wlog[o] = expf(-0.60653065971263342f * sigmoidf_(wlog[o] + ldf(w_bias + h * dk + i)));
+  }
+}
+
+__device__ __forceinline__ void cp_async4(float* dst_smem, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst_smem)), "l"(src) : "memory");
+}
+
+template <int KPT, int P>
+__global__ void delta_rule_kernel(const float* __restrict__ proj, int ld, int col_r, int col_k, int col_v, const float* __restrict__ wdec,
+                                  const float* __restrict__ uvec, const float* __restrict__ auvec, const Item* __restrict__ seqs, int H, int dk,
                                   int dv, float* __restrict__ state, size_t state_slot_stride, float* __restrict__ o_raw) {
-  constexpr int CH = 8;
-  constexpr int DKP = KPT * P;                       // padded key size
-  __shared__ float s_w[CH][DKP], s_au[CH][DKP], s_u[CH][DKP], s_k[CH][DKP], s_r[CH][DKP];
-  extern __shared__ float s_v[];                     // [CH][dv]
+  constexpr int DKP = KPT * P;                       // padded key size (>= dk, and >= dv: the design uses one size for both)
+  constexpr int CH = DKP <= 64 ? 16 : DKP <= 128 ? 8 : 4;   // tokens per buffer: two buffers fill the 48 KB of static shared memory
+  __shared__ float buf[2][CH][6][DKP];               // per token: w, a*u, u, k, r, v
   const Item sq = seqs[blockIdx.x / H];
   const int h = blockIdx.x % H;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -298,48 +377,55 @@ __global__ void delta_rule_kernel(const float* __restrict__ proj, int ld, int co
     const int i = e * P + part;
     s[e] = (col_ok && i < dk) ? S[(size_t)i * dv + col] : 0.f;
   }
-  for (int t0 = 0; t0 < sq.n_rows; t0 += CH) {
-    const int nt = min(CH, sq.n_rows - t0);
-    __syncthreads();
-    // stage: one warp per token computes the head's vectors
-    for (int t = warp; t < nt; t += (blockDim.x >> 5)) {
+  for (int e = threadIdx.x; e < 2 * CH * 6 * DKP; e += blockDim.x) (&buf[0][0][0][0])[e] = 0.f;   // the padding stays zero
+  __syncthreads();
+  const int HD = H * dk;
+  auto issue = [&](int c) {
+    const int t0 = c * CH, nt = min(CH, sq.n_rows - t0);
+    for (int e = threadIdx.x; e < nt * 6 * dk; e += blockDim.x) {
+      const int t = e / (6 * dk), rem = e % (6 * dk), vec = rem / dk, i = rem % dk;
       const size_t m = (size_t)sq.row0 + t0 + t;
-      const float* pr = proj + m * ld;
-      float ss = 0.f;
-      for (int i = lane; i < dk; i += 32) { const float kv = pr[col_k + h * dk + i]; ss = fmaf(kv, kv, ss); }
-      const float inv = 1.0f / sqrtf(warp_sum(ss) + 1e-6f);
-      for (int i = lane; i < DKP; i += 32) {
-        float w = 0.f, au = 0.f, u = 0.f, kk = 0.f, rr = 0.f;
-        if (i < dk) {
-          kk = pr[col_k + h * dk + i];
-          rr = pr[col_r + h * dk + i];
-          u = kk * inv;
-          au = sigmoidf_(pr[col_a + h * dk + i] + ldf(a_bias + h * dk + i)) * u;
-          w = expf(-0.60653065971263342f * sigmoidf_(wlog[m * (size_t)(H * dk) + h * dk + i] + ldf(w_bias + h * dk + i)));
-        }
-        s_w[t][i] = w; s_au[t][i] = au; s_u[t][i] = u; s_k[t][i] = kk; s_r[t][i] = rr;
-      }
-      for (int j = lane; j < dv; j += 32) s_v[t * dv + j] = pr[col_v + h * dv + j];
+      const float* src = vec == 0 ? wdec + m * HD + h * dk + i
+                       : vec == 1 ? auvec + m * HD + h * dk + i
+                       : vec == 2 ? uvec + m * HD + h * dk + i
+                       : vec == 3 ? proj + m * ld + col_k + h * dk + i
+                       : vec == 4 ? proj + m * ld + col_r + h * dk + i
+                                  : proj + m * ld + col_v + h * dv + i;
+      cp_async4(&buf[c & 1][t][vec][i], src);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  const int nch = (sq.n_rows + CH - 1) / CH;
+  issue(0);
+  for (int c = 0; c < nch; ++c) {
+    if (c + 1 < nch) {
+      issue(c + 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     __syncthreads();
+    const int nt = min(CH, sq.n_rows - c * CH);
+    float(*b)[6][DKP] = buf[c & 1];
     for (int t = 0; t < nt; ++t) {
       float dot = 0.f;
 #pragma unroll
-      for (int e = 0; e < KPT; ++e) dot = fmaf(s_u[t][e * P + part], s[e], dot);
+      for (int e = 0; e < KPT; ++e) dot = fmaf(b[t][2][e * P + part], s[e], dot);
 #pragma unroll
       for (int o = P / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-      const float vj = col_ok ? s_v[t * dv + col] : 0.f;
+      const float vj = col_ok ? b[t][5][col] : 0.f;
       float out = 0.f;
 #pragma unroll
       for (int e = 0; e < KPT; ++e) {
         const int i = e * P + part;
-        s[e] = fmaf(s_w[t][i], s[e], fmaf(-s_au[t][i], dot, s_k[t][i] * vj));
-        out = fmaf(s[e], s_r[t][i], out);
+        s[e] = fmaf(b[t][0][i], s[e], fmaf(-b[t][1][i], dot, b[t][3][i] * vj));
+        out = fmaf(s[e], b[t][4][i], out);
       }
 #pragma unroll
       for (int o = P / 2; o > 0; o >>= 1) out += __shfl_xor_sync(0xffffffffu, out, o);
-      if (col_ok && part == 0) o_raw[((size_t)sq.row0 + t0 + t) * (size_t)(H * dv) + h * dv + col] = out;
+      if (col_ok && part == 0) o_raw[((size_t)sq.row0 + c * CH + t) * (size_t)(H * dv) + h * dv + col] = out;
     }
+    __syncthreads();                                 // the buffer is refilled two chunks later
   }
 #pragma unroll
   for (int e = 0; e < KPT; ++e) {

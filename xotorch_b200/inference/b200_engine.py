@@ -120,8 +120,8 @@ class B200ShardInferenceEngine(InferenceEngine):
   def _make_native(self, hf_config: dict):
     if self._native_factory is not None:
       return self._native_factory(hf_config, self.device)
-    from xotorch_b200.native import NativeShard             # raises ImportError if libxotb200.so is missing
-    return NativeShard(hf_config, self.device)
+    from xotorch_b200.models import make_native             # the registry picks the native engine of the model's family;
+    return make_native(hf_config, self.device)              # raises ImportError if its library is missing
 
   # ---- device-resident hop ---------------------------------------------------------------------------------------
   def attach_next_engine(self, nxt: Optional["B200ShardInferenceEngine"]) -> None:
@@ -146,12 +146,13 @@ class B200ShardInferenceEngine(InferenceEngine):
     """sharded_inference_engine.py:372-421: no-op for the same shard, else (re)load config, tokenizer, weights."""
     if self.shard == shard:
       return
-    from xotorch_b200.native import load_hf_config
+    from xotorch_b200.models import load_model_config, model_summary
     self.model_path = Path(await self.shard_downloader.ensure_shard(shard, self.__class__.__name__))
-    self.model_config = load_hf_config(self.model_path)
-    if self.model_config["num_hidden_layers"] != shard.n_layers:
-      raise ValueError(f"shard.n_layers={shard.n_layers} but the model has {self.model_config['num_hidden_layers']} layers")
-    self.tokenizer = resolve_local_tokenizer(self.model_path, self.model_config["vocab_size"])
+    self.model_config = load_model_config(self.model_path)
+    self.model_info = model_summary(self.model_config)      # depth / vocabulary / width / context whatever the config's dialect
+    if self.model_info["n_layers"] != shard.n_layers:
+      raise ValueError(f"shard.n_layers={shard.n_layers} but the model has {self.model_info['n_layers']} layers")
+    self.tokenizer = resolve_local_tokenizer(self.model_path, self.model_info["vocab"])
 
     def start_model():
       if self.native is not None:
@@ -195,8 +196,8 @@ class B200ShardInferenceEngine(InferenceEngine):
       raise ValueError(f"input_data.ndim must be 2 (token ids) or 3 (hidden state), got {input_data.ndim}")
     start_pos = int(inference_state["curr_pos"]) if inference_state and "curr_pos" in inference_state else 0
     hop_in = parse_hop_descriptor(input_data)               # the previous shard already put the hidden state into our HBM
-    if hop_in is not None and hop_in[2] != self.model_config["hidden_size"]:
-      raise ValueError(f"hop descriptor for hidden size {hop_in[2]} reached a model of hidden size {self.model_config['hidden_size']}")
+    if hop_in is not None and hop_in[2] != self.model_info["width"]:
+      raise ValueError(f"hop descriptor for hidden size {hop_in[2]} reached a model of hidden size {self.model_info['width']}")
     n = hop_in[1] if hop_in is not None else input_data.shape[1]
     self.request_id = request_id
 
@@ -217,12 +218,12 @@ class B200ShardInferenceEngine(InferenceEngine):
       if last:
         return logits
       self.hop_stats["device_out"] += 1
-      return make_hop_descriptor(seq_out, n, self.model_config["hidden_size"])
+      return make_hop_descriptor(seq_out, n, self.model_info["width"])
 
     def step():
       # KV capacity = prompt + 1024 like the reference (general_mha.py:152), clamped to the model's context: a prompt that fits
       # the context must not be refused because prompt + 1024 does not
-      max_pos = int(self.model_config["max_position_embeddings"])
+      max_pos = int(self.model_info["max_positions"])
       if start_pos + n > max_pos:
         raise RuntimeError(f"{start_pos + n} positions exceed the model's context of {max_pos} (max_position_embeddings)")
       need = min(max(n + MAX_GENERATED_TOKENS, int((inference_state or {}).get("max_total_len", 0))), max_pos)
