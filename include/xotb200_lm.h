@@ -120,6 +120,9 @@ int xotb200_lm_read_trace(xotb200_lm* e, float* out, int64_t n_floats);
 int xotb200_lm_set_gemm_mode(xotb200_lm* e, int mode);
 
 int xotb200_lm_kernel_launches(xotb200_lm* e, int64_t* count);
+/* Decode steps (every request brings one row) are captured into CUDA graphs and replayed: 1 = on (default), 0 = off. */
+int xotb200_lm_set_graphs(xotb200_lm* e, int on);
+int xotb200_lm_graph_replays(xotb200_lm* e, int64_t* count);
 /* Attention kernel choice in the bf16 mode: 0 = automatic (a request that brings 16 rows or more: expanded keys / values and the
  * tensor-core streaming-softmax kernel; fewer rows: the absorbed kernel over the latent rows), 1 = always the absorbed kernel. */
 int xotb200_lm_set_attention_mode(xotb200_lm* e, int mode);

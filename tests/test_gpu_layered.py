@@ -385,3 +385,39 @@ def test_expanded_prompt_attention_equals_the_absorbed_kernel(sizes):
   assert n.prompt_attention_launches() - before == 4
   assert row_err(got_a, absorbed.astype(np.float64)) < 0.03
   n.close()
+
+
+# ---- decode steps replayed from CUDA graphs ----------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_graph_replay_of_decode_steps_changes_nothing(dtype):
+  """a decode step is captured the second time its shape is seen and replayed afterwards; lengths, pages, slots and wanted rows
+  live in device arrays that every replay refreshes — so the logits equal those of plain launches bit for bit, across page
+  borders, across the 256-token length bucket, and when a request leaves the batch"""
+  cfg = config(MIXED)
+  W = zo.random_weights(cfg, 19)
+  seqs = [rand_tokens(cfg["vocab"], 300, 40 + i) for i in range(3)]
+  starts = [240, 3, 17]
+
+  def run(graphs):
+    n = make_engine(cfg, W, dtype, max_tokens=1000, max_requests=3, page_size=8)
+    n.set_graphs(graphs)
+    n.step([0, 1, 2], [s[:k] for s, k in zip(seqs, starts)])
+    out, live = [], [0, 1, 2]
+    for t in range(40):
+      if t == 25:
+        live = [0, 2]
+        n.clear_request(1)
+      lg, _ = n.step(live, [seqs[i][starts[i] + t:starts[i] + t + 1] for i in live])
+      out.append(lg)
+    replays = n.graph_replays()
+    n.close()
+    return out, replays
+
+  plain, r0 = run(False)
+  replayed, r1 = run(True)
+  assert r0 == 0 and r1 >= 30
+  for a, b in zip(plain, replayed):
+    assert np.array_equal(a, b)
+  ref = oracle_logits(cfg, W, seqs[0][:280])[0]
+  got = np.stack([x[0] for x in replayed])
+  assert row_err(got, ref[240:280]) < TOL[dtype]

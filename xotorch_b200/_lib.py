@@ -139,6 +139,8 @@ _LM_SIGS = {
   "xotb200_lm_read_trace": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64]),
   "xotb200_lm_set_gemm_mode": (C.c_int, [C.c_void_p, C.c_int]),
   "xotb200_lm_kernel_launches": (C.c_int, [C.c_void_p, C.POINTER(C.c_int64)]),
+  "xotb200_lm_set_graphs": (C.c_int, [C.c_void_p, C.c_int]),
+  "xotb200_lm_graph_replays": (C.c_int, [C.c_void_p, C.POINTER(C.c_int64)]),
   "xotb200_lm_set_attention_mode": (C.c_int, [C.c_void_p, C.c_int]),
   "xotb200_lm_prompt_attention_launches": (C.c_int, [C.c_void_p, C.POINTER(C.c_int64)]),
   "xotb200_lm_tensor_core_launches": (C.c_int, [C.c_void_p, C.POINTER(C.c_int64)]),

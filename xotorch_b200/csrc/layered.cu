@@ -19,6 +19,7 @@
 #include <unistd.h>
 
 #include <algorithm>
+#include <array>
 #include <type_traits>
 #include <map>
 #include <string>
@@ -87,6 +88,12 @@ struct LmLayer {
   size_t state_off = 0;                                // delta rule: float offset of this layer's state inside a slot's block
 };
 
+struct GraphSlot {
+  int seen = 0;
+  cudaGraphExec_t exec = nullptr;
+  int64_t launches = 0;
+};
+
 struct xotb200_lm {
   xotb200_lm_cfg cfg;
   std::vector<LmLayer> layers;                         // local layers
@@ -127,6 +134,9 @@ struct xotb200_lm {
   float* trace_buf = nullptr;
   size_t trace_floats = 0, trace_cap = 0;
   int gemm_mode = 0;
+  bool graphs_on = true;                               // decode steps are replayed from CUDA graphs
+  std::map<std::array<long, 5>, GraphSlot> graphs;
+  int64_t graph_replays = 0;
   bool flash_on = true;                                // bf16: prompt portions of FLASH_MIN_ROWS rows or more use the expanded tensor-core attention
   std::vector<int> stage_build;
   int64_t launches = 0, tc_launches = 0, flash_launches = 0;
@@ -347,10 +357,22 @@ static int product(xotb200_lm* e, const TA* A, long lda, long a_batch, const TB*
     }
   }
   if (e->gemm_mode == 0 && M <= 8 && sbk == 1 && smem <= GEMV_SMEM_MAX) {
-    auto kern = gemv_rows_kernel<TA, TB, TC, EPI, 8>;
-    TRY(opt_in_smem(kern, smem));
-    const int blocks = std::max(1, std::min(cdiv(N, 8), e->sm_count * 4 / std::max(1, batch)));
-    kern<<<dim3(blocks, 1, batch), 256, smem, e->stream>>>(A, lda, a_batch, B, sbn, b_batch, C, ldc, c_batch, M, N, K);
+    // warps per row group: enough K per warp to keep its lanes busy, more slices when there are few rows
+    int wsplit = 1;
+    while (wsplit < 8 && K / (wsplit * 2) >= 256 && (long)cdiv(N, 4 * (8 / wsplit)) * batch < 4L * e->sm_count) wsplit *= 2;
+    const int blocks = std::max(1, std::min(cdiv(N, 4 * (8 / wsplit)), e->sm_count * 8 / std::max(1, batch)));
+    const size_t sm = smem + 8 * 4 * 8 * 4;
+#define LAUNCH_GEMV(MR)                                                                                                        \
+  do {                                                                                                                         \
+    auto kern = gemv_rows_kernel<TA, TB, TC, EPI, MR>;                                                                         \
+    TRY(opt_in_smem(kern, sm));                                                                                                \
+    kern<<<dim3(blocks, 1, batch), 256, sm, e->stream>>>(A, lda, a_batch, B, sbn, b_batch, C, ldc, c_batch, M, N, K, wsplit); \
+  } while (0)
+    if (M == 1) LAUNCH_GEMV(1);
+    else if (M == 2) LAUNCH_GEMV(2);
+    else if (M <= 4) LAUNCH_GEMV(4);
+    else LAUNCH_GEMV(8);
+#undef LAUNCH_GEMV
   } else {
     gemm_tiled_kernel<TA, TB, TC, EPI><<<dim3(cdiv(N, 64), cdiv(M, 64), batch), 256, 0, e->stream>>>(A, lda, a_batch, B, sbn, sbk, b_batch, C, ldc,
                                                                                                   c_batch, M, N, K);
@@ -370,9 +392,17 @@ template <typename P> static int regrow(P*& p, size_t bytes) {
   return 0;
 }
 
+// captured decode steps hold device pointers: whenever a buffer they name is replaced they are dropped
+static void drop_graphs(xotb200_lm* e) {
+  for (auto& kv : e->graphs)
+    if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
+  e->graphs.clear();
+}
+
 static int ensure_scratch(xotb200_lm* e, int M, int n_want) {
   const int D = e->cfg.width;
   if (M > e->m_cap) {
+    drop_graphs(e);
     const size_t m = (size_t)std::max(M, 64), z = e->esz;
     TRY(regrow(e->x, m * D * 4));
     TRY(regrow(e->y, m * D * 4));
@@ -395,6 +425,7 @@ static int ensure_scratch(xotb200_lm* e, int M, int n_want) {
     e->trace_cap = 0;
   }
   if (n_want > e->want_cap) {
+    drop_graphs(e);
     const size_t w = (size_t)std::max(n_want, 16);
     TRY(regrow(e->hw, w * D * e->esz));
     TRY(regrow(e->logits, w * e->cfg.vocab * 4));
@@ -410,6 +441,7 @@ static int ensure_scratch(xotb200_lm* e, int M, int n_want) {
 
 static int ensure_host_out(xotb200_lm* e, size_t floats) {
   if (floats <= e->h_out_cap) return 0;
+  drop_graphs(e);
   if (e->h_out) { cudaFreeHost(e->h_out); e->h_out = nullptr; }
   CK(cudaHostAlloc(&e->h_out, floats * 4, cudaHostAllocDefault));
   e->h_out_cap = floats;
@@ -488,7 +520,7 @@ static int attention_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
       splits = cdiv(span, chunk);
       if (splits > 1) {
         const size_t need = (size_t)M * H * splits * (2 + R);
-        if (need > e->part_cap) { TRY(regrow(e->part, need * 4)); e->part_cap = need; }
+        if (need > e->part_cap) { drop_graphs(e); TRY(regrow(e->part, need * 4)); e->part_cap = need; }
       }
       const dim3 grid(it.second, cdiv(pairs, nw), splits);
 #define LAUNCH_ATTN(NACC)                                                                                                                       \
@@ -636,7 +668,7 @@ static int run_layers(xotb200_lm* e, const StepPlan& sp, int n_want) {
     CK(cudaGetLastError());
     e->launches++;
     TRY((product<T, T, float, 0>(e, hw, D, 0, at<T>(e, e->head), D, 1, 0, e->logits, e->cfg.vocab, 0, n_want, e->cfg.vocab, D, 1)));
-    argmax_rows_kernel<<<n_want, 256, 0, e->stream>>>(e->logits, e->cfg.vocab, e->d_argmax);
+    argmax_rows_kernel<<<n_want, 1024, 0, e->stream>>>(e->logits, e->cfg.vocab, e->d_argmax);
     CK(cudaGetLastError());
     e->launches++;
   }
@@ -716,6 +748,7 @@ int xotb200_lm_destroy(xotb200_lm* e) {
   if (!e) return 0;
   cudaSetDevice(e->device);
   if (e->stream) cudaStreamSynchronize(e->stream);
+  drop_graphs(e);
   free_state(e);
   for (auto& L : e->layers)
     if (L.freqs) cudaFree(L.freqs);
@@ -853,6 +886,7 @@ int xotb200_lm_begin(xotb200_lm* e, int max_tokens, int max_requests, int page_s
   REQUIRE(page_size >= 0 && page_size <= 4096, "page_size out of range");
   CK(cudaSetDevice(e->device));
   CK(cudaStreamSynchronize(e->stream));
+  drop_graphs(e);
   free_state(e);
   const int P = page_size > 0 ? page_size : 64;
   e->page_size = P;
@@ -1013,6 +1047,7 @@ int xotb200_lm_step(xotb200_lm* e, int n_seq, const int32_t* slots, const int32_
   }
   const size_t off = st.size();
   if (off > e->stage_cap) {
+    drop_graphs(e);
     CK(cudaStreamSynchronize(e->stream));
     if (e->h_stage) cudaFreeHost(e->h_stage);
     if (e->d_stage) cudaFree(e->d_stage);
@@ -1023,36 +1058,73 @@ int xotb200_lm_step(xotb200_lm* e, int n_seq, const int32_t* slots, const int32_
     e->stage_cap = cap;
   }
   memcpy(e->h_stage, st.data(), off * 4);
-  CK(cudaEventRecord(e->ev0, e->stream));
-  CK(cudaMemcpyAsync(e->d_stage, e->h_stage, off * 4, cudaMemcpyHostToDevice, e->stream));
-  sp.tokens = e->d_stage;
-  sp.row_slot = e->d_stage + M;
-  sp.row_pos = e->d_stage + 2 * M;
-  sp.want = e->d_stage + 3 * M;
-  sp.seqs = reinterpret_cast<const Item*>(e->d_stage + off_seqs);
-  for (auto& kv : item_off) sp.items[kv.first] = {reinterpret_cast<const Item*>(e->d_stage + kv.second.first), kv.second.second};
-  for (auto& kv : flash_off) {
-    StepPlan::Flash f;
-    f.reqs = reinterpret_cast<const GatherReq*>(e->d_stage + kv.second.reqs);
-    f.tiles = reinterpret_cast<const FlashTile*>(e->d_stage + kv.second.tiles);
-    f.n_reqs = kv.second.n_reqs; f.n_tiles = kv.second.n_tiles; f.n_keys = kv.second.n_keys; f.max_keys = kv.second.max_keys;
-    sp.flash[kv.first] = f;
+  if (e->last && n_want > 0) TRY(ensure_host_out(e, (size_t)n_want * V + n_want));
+  else if (!e->last) TRY(ensure_host_out(e, (size_t)M * D));
+  // Decoding — every request brings one row — has the same launches step after step: only the contents of the index arrays and
+  // the lengths differ.  Such a step is captured into a CUDA graph the second time its shape is seen and replayed from then on.
+  // What the launches depend on is in the key; the key length is a bucket of the longest request (it fixes how the absorbed
+  // attention kernel cuts the keys into runs).
+  const bool decode_shape = e->graphs_on && e->first && !e->trace && M == n_seq;
+  sp.max_len = decode_shape ? cdiv(sp.max_len, 256) * 256 : sp.max_len;
+  GraphSlot* gs = nullptr;
+  if (decode_shape) {
+    const std::array<long, 5> key{n_seq, n_want, (logits_f32 ? 1 : 0) | (argmax_i32 ? 2 : 0), sp.max_len, (long)off};
+    gs = &e->graphs[key];
   }
-  if (!e->first) CK(cudaMemcpyAsync(e->x, hidden_f32, (size_t)M * D * 4, cudaMemcpyHostToDevice, e->stream));
-  {
-    int rc = e->esz == 2 ? run_layers<bf16>(e, sp, n_want) : run_layers<float>(e, sp, n_want);
+  CK(cudaEventRecord(e->ev0, e->stream));
+  if (gs && gs->exec) {
+    CK(cudaGraphLaunch(gs->exec, e->stream));
+    e->launches += gs->launches;
+    e->graph_replays++;
+  } else {
+    const bool capture = gs && gs->seen >= 1;
+    if (gs) gs->seen++;
+    const int64_t launches0 = e->launches;
+    if (capture) CK(cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeRelaxed));
+    int rc = 0;
+    auto body = [&]() -> int {
+      CK(cudaMemcpyAsync(e->d_stage, e->h_stage, off * 4, cudaMemcpyHostToDevice, e->stream));
+      sp.tokens = e->d_stage;
+      sp.row_slot = e->d_stage + M;
+      sp.row_pos = e->d_stage + 2 * M;
+      sp.want = e->d_stage + 3 * M;
+      sp.seqs = reinterpret_cast<const Item*>(e->d_stage + off_seqs);
+      for (auto& kv : item_off) sp.items[kv.first] = {reinterpret_cast<const Item*>(e->d_stage + kv.second.first), kv.second.second};
+      for (auto& kv : flash_off) {
+        StepPlan::Flash f;
+        f.reqs = reinterpret_cast<const GatherReq*>(e->d_stage + kv.second.reqs);
+        f.tiles = reinterpret_cast<const FlashTile*>(e->d_stage + kv.second.tiles);
+        f.n_reqs = kv.second.n_reqs; f.n_tiles = kv.second.n_tiles; f.n_keys = kv.second.n_keys; f.max_keys = kv.second.max_keys;
+        sp.flash[kv.first] = f;
+      }
+      if (!e->first) CK(cudaMemcpyAsync(e->x, hidden_f32, (size_t)M * D * 4, cudaMemcpyHostToDevice, e->stream));
+      TRY(e->esz == 2 ? run_layers<bf16>(e, sp, n_want) : run_layers<float>(e, sp, n_want));
+      if (e->last && n_want > 0) {
+        if (logits_f32) CK(cudaMemcpyAsync(e->h_out, e->logits, (size_t)n_want * V * 4, cudaMemcpyDeviceToHost, e->stream));
+        if (argmax_i32) CK(cudaMemcpyAsync(e->h_out + (size_t)n_want * V, e->d_argmax, (size_t)n_want * 4, cudaMemcpyDeviceToHost, e->stream));
+      } else if (!e->last) {
+        CK(cudaMemcpyAsync(e->h_out, e->x, (size_t)M * D * 4, cudaMemcpyDeviceToHost, e->stream));
+      }
+      CK(cudaMemcpyAsync(e->h_err, e->d_err, 4, cudaMemcpyDeviceToHost, e->stream));
+      return 0;
+    };
+    rc = body();
+    if (capture) {
+      cudaGraph_t graph = nullptr;
+      cudaError_t ce = cudaStreamEndCapture(e->stream, &graph);
+      if (rc == 0 && ce == cudaSuccess && graph && cudaGraphInstantiate(&gs->exec, graph, 0) == cudaSuccess) {
+        gs->launches = e->launches - launches0;
+        ce = cudaGraphLaunch(gs->exec, e->stream);
+      } else if (rc == 0) {
+        gs->exec = nullptr;
+        set_err("capturing the decode step into a CUDA graph failed: %s", cudaGetErrorString(ce != cudaSuccess ? ce : cudaGetLastError()));
+        rc = XOTB200_ECUDA;
+      }
+      if (graph) cudaGraphDestroy(graph);
+      if (rc == 0 && ce != cudaSuccess) { set_err("launching the captured decode step failed: %s", cudaGetErrorString(ce)); rc = XOTB200_ECUDA; }
+    }
     if (rc < 0) { cudaStreamSynchronize(e->stream); return rc; }
   }
-  // ---- results
-  if (e->last && n_want > 0) {
-    TRY(ensure_host_out(e, (size_t)n_want * V + n_want));
-    if (logits_f32) CK(cudaMemcpyAsync(e->h_out, e->logits, (size_t)n_want * V * 4, cudaMemcpyDeviceToHost, e->stream));
-    if (argmax_i32) CK(cudaMemcpyAsync(e->h_out + (size_t)n_want * V, e->d_argmax, (size_t)n_want * 4, cudaMemcpyDeviceToHost, e->stream));
-  } else if (!e->last) {
-    TRY(ensure_host_out(e, (size_t)M * D));
-    CK(cudaMemcpyAsync(e->h_out, e->x, (size_t)M * D * 4, cudaMemcpyDeviceToHost, e->stream));
-  }
-  CK(cudaMemcpyAsync(e->h_err, e->d_err, 4, cudaMemcpyDeviceToHost, e->stream));
   CK(cudaEventRecord(e->ev1, e->stream));
   CK(cudaStreamSynchronize(e->stream));
   CK(cudaEventElapsedTime(&e->last_ms, e->ev0, e->ev1));
@@ -1088,6 +1160,7 @@ int xotb200_lm_read_trace(xotb200_lm* e, float* out, int64_t n_floats) {
 
 int xotb200_lm_set_gemm_mode(xotb200_lm* e, int mode) {
   REQUIRE(e && mode >= 0 && mode <= 2, "gemm mode must be 0, 1 or 2");
+  drop_graphs(e);
   e->gemm_mode = mode;
   return 0;
 }
@@ -1098,8 +1171,22 @@ int xotb200_lm_kernel_launches(xotb200_lm* e, int64_t* count) {
   return 0;
 }
 
+int xotb200_lm_set_graphs(xotb200_lm* e, int on) {
+  REQUIRE(e, "null engine");
+  drop_graphs(e);
+  e->graphs_on = on != 0;
+  return 0;
+}
+
+int xotb200_lm_graph_replays(xotb200_lm* e, int64_t* count) {
+  REQUIRE(e && count, "null argument");
+  *count = e->graph_replays;
+  return 0;
+}
+
 int xotb200_lm_set_attention_mode(xotb200_lm* e, int mode) {
   REQUIRE(e && mode >= 0 && mode <= 1, "attention mode must be 0 or 1");
+  drop_graphs(e);
   e->flash_on = mode == 0;
   return 0;
 }

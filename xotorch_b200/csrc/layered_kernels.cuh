@@ -521,54 +521,85 @@ gemm_tiled_kernel(const TA* __restrict__ A, long lda, long a_batch, const TB* __
     }
 }
 
-// gemv_rows_kernel: the decode form (M <= MR rows, B contiguous along k).  One warp per output column n: the weight row is read
-// ONCE, 16 bytes per lane per step, and multiplied into all M activation rows (held in shared memory as fp32).
+// gemv_rows_kernel: the decode form (M <= MR activation rows, B contiguous along k).  The weights are read ONCE, 16 bytes per
+// lane per load, and multiplied into all M activation rows (held in shared memory as fp32).  To keep enough loads in flight for
+// HBM, a warp works on RB = 4 weight rows at a time (four independent loads per step) and `wsplit` warps share a row group by
+// cutting K into slices (a [N small, K large] matrix still fills the GPU); the slices meet in shared memory.
 template <typename TA, typename TB, typename TC, int EPI, int MR>
 __global__ void __launch_bounds__(256)
 gemv_rows_kernel(const TA* __restrict__ A, long lda, long a_batch, const TB* __restrict__ B, long sbn, long b_batch, TC* __restrict__ C, long ldc,
-                 long c_batch, int M, int N, int K) {
-  extern __shared__ float a_s[];                     // [M][K]
+                 long c_batch, int M, int N, int K, int wsplit) {
+  constexpr int RB = 4;
+  extern __shared__ float a_s[];                     // [M][K], then the slice sums [8 warps][RB][MR]
   A += (size_t)blockIdx.z * a_batch;
   B += (size_t)blockIdx.z * b_batch;
   C += (size_t)blockIdx.z * c_batch;
-  for (int e = threadIdx.x; e < M * K; e += blockDim.x) a_s[e] = ldf(A + (size_t)(e / K) * lda + e % K);
+  for (int m = 0; m < M; ++m)
+    for (int k = threadIdx.x; k < K; k += blockDim.x) a_s[m * K + k] = ldf(A + (size_t)m * lda + k);
+  float* red = a_s + (size_t)M * K;
   __syncthreads();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int gpb = 8 / wsplit, grp = warp / wsplit, slice = warp % wsplit;
   constexpr int VEC = 16 / sizeof(TB);
-  for (int n = blockIdx.x * nw + warp; n < N; n += gridDim.x * nw) {
-    const TB* b = B + (size_t)n * sbn;
-    float acc[MR];
+  const bool vec_ok = (K % VEC == 0) && (sbn % VEC == 0) && ((reinterpret_cast<uintptr_t>(B) & 15) == 0);
+  const int step = vec_ok ? 32 * VEC : 32;
+  const int ksl = ((K + wsplit - 1) / wsplit + step - 1) / step * step;
+  const int kbeg = slice * ksl, kend = min(K, kbeg + ksl);
+  for (int nb = blockIdx.x * gpb * RB; nb < N; nb += gridDim.x * gpb * RB) {   // uniform trip count for the whole block
+    const int n0 = nb + grp * RB;
+    float acc[RB][MR];
 #pragma unroll
-    for (int m = 0; m < MR; ++m) acc[m] = 0.f;
-    const bool vec_ok = (K % VEC == 0) && ((reinterpret_cast<uintptr_t>(b) & 15) == 0);
+    for (int r = 0; r < RB; ++r)
+#pragma unroll
+      for (int m = 0; m < MR; ++m) acc[r][m] = 0.f;
     if (vec_ok) {
-      for (int k = lane * VEC; k < K; k += 32 * VEC) {
-        const uint4 raw = *reinterpret_cast<const uint4*>(b + k);
-        const TB* bv = reinterpret_cast<const TB*>(&raw);
+      for (int k = kbeg + lane * VEC; k < kend; k += 32 * VEC) {
+        uint4 raw[RB];
+#pragma unroll
+        for (int r = 0; r < RB; ++r)
+          raw[r] = n0 + r < N ? *reinterpret_cast<const uint4*>(B + (size_t)(n0 + r) * sbn + k) : make_uint4(0, 0, 0, 0);
 #pragma unroll
         for (int v = 0; v < VEC; ++v) {
-          const float w = ldf(bv + v);
+          float av[MR];
 #pragma unroll
-          for (int m = 0; m < MR; ++m)
-            if (m < M) acc[m] = fmaf(a_s[m * K + k + v], w, acc[m]);
+          for (int m = 0; m < MR; ++m) av[m] = m < M ? a_s[m * K + k + v] : 0.f;
+#pragma unroll
+          for (int r = 0; r < RB; ++r) {
+            const float w = ldf(reinterpret_cast<const TB*>(&raw[r]) + v);
+#pragma unroll
+            for (int m = 0; m < MR; ++m) acc[r][m] = fmaf(av[m], w, acc[r][m]);
+          }
         }
       }
     } else {
-      for (int k = lane; k < K; k += 32) {
-        const float w = ldf(b + k);
+      for (int k = kbeg + lane; k < kend; k += 32) {
 #pragma unroll
-        for (int m = 0; m < MR; ++m)
-          if (m < M) acc[m] = fmaf(a_s[m * K + k], w, acc[m]);
+        for (int r = 0; r < RB; ++r) {
+          const float w = n0 + r < N ? ldf(B + (size_t)(n0 + r) * sbn + k) : 0.f;
+#pragma unroll
+          for (int m = 0; m < MR; ++m)
+            if (m < M) acc[r][m] = fmaf(a_s[m * K + k], w, acc[r][m]);
+        }
       }
     }
 #pragma unroll
-    for (int m = 0; m < MR; ++m) {
-      float v = warp_sum(acc[m]);
-      if (m < M && lane == 0) {
+    for (int r = 0; r < RB; ++r)
+#pragma unroll
+      for (int m = 0; m < MR; ++m) {
+        const float v = warp_sum(acc[r][m]);
+        if (lane == 0) red[(warp * RB + r) * MR + m] = v;
+      }
+    __syncthreads();
+    if (slice == 0 && lane < RB * MR) {
+      const int r = lane / MR, m = lane % MR;
+      float v = 0.f;
+      for (int sidx = 0; sidx < wsplit; ++sidx) v += red[((warp + sidx) * RB + r) * MR + m];   // fixed order: deterministic
+      if (m < M && n0 + r < N) {
         if (EPI == 1) { v = fmaxf(v, 0.f); v *= v; }
-        stf(C + (size_t)m * ldc + n, v);
+        stf(C + (size_t)m * ldc + n0 + r, v);
       }
     }
+    __syncthreads();
   }
 }
 

@@ -285,6 +285,14 @@ class LayeredShard:
     check_lm(self.lib.xotb200_lm_kernel_launches(self.h, C.byref(v)))
     return int(v.value)
 
+  def set_graphs(self, on: bool):
+    check_lm(self.lib.xotb200_lm_set_graphs(self.h, 1 if on else 0))
+
+  def graph_replays(self) -> int:
+    v = C.c_int64()
+    check_lm(self.lib.xotb200_lm_graph_replays(self.h, C.byref(v)))
+    return int(v.value)
+
   def set_attention_mode(self, mode: int):
     check_lm(self.lib.xotb200_lm_set_attention_mode(self.h, int(mode)))
 
