@@ -286,6 +286,9 @@ static bool owned_name(const xotb200_lm* e, const std::string& name) {
 // products
 // ---------------------------------------------------------------------------------------------------------------------------
 static const size_t GEMV_SMEM_MAX = 160 * 1024;
+// Rows up to which 16-bit products run on the one-warp-per-row-group kernel.  Beyond two rows its fp32 FMAs (8 per weight at 8
+// rows) fall behind the weight stream, and the tensor-core tiles — mostly empty, but they read each weight once — are faster.
+static const int GEMV_MAX_ROWS = 2;
 
 template <typename K>
 static int opt_in_smem(K kernel, size_t bytes) {
@@ -335,7 +338,7 @@ static int launch_ltc(xotb200_lm* e, const CUtensorMap& ma, const CUtensorMap& m
 template <typename TC, int EPI>
 static int product_tc(xotb200_lm* e, const bf16* A, long lda, long a_batch, const bf16* B, long ldb, long b_batch, TC* C, long ldc, long c_batch, int M,
                       int N, int K, int batch) {
-  const int nt = N > 64 ? 128 : 64;
+  const int nt = (N > 64 && M > LTC_M) ? 128 : 64;   // one row tile: narrower column tiles, twice the CTAs streaming weights
   CUtensorMap ma, mb;
   if (!make_map3(&ma, A, M, K, lda, a_batch, batch, LTC_M) || !make_map3(&mb, B, N, K, ldb, b_batch, batch, nt)) return 0;
   LtcArgs a{M, N, K, C, ldc, c_batch, e->d_err};
@@ -351,7 +354,7 @@ static int product(xotb200_lm* e, const TA* A, long lda, long a_batch, const TB*
   const size_t smem = (size_t)M * K * 4;
   if constexpr (std::is_same<TA, bf16>::value && std::is_same<TB, bf16>::value && (EPI == 0 || !std::is_same<TC, float>::value)) {
     // 16-bit operands with more rows than the decode kernel takes: the tensor cores, when the operands can be described to TMA
-    if (sbk == 1 && ((e->gemm_mode == 0 && M > 8) || e->gemm_mode == 2)) {
+    if (sbk == 1 && ((e->gemm_mode == 0 && M > GEMV_MAX_ROWS) || e->gemm_mode == 2)) {
       const int r = product_tc<TC, EPI>(e, A, lda, a_batch, B, sbn, b_batch, C, ldc, c_batch, M, N, K, batch);
       if (r != 0) return r < 0 ? r : 0;
     }
@@ -515,7 +518,8 @@ static int attention_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
       // few work items (decoding): cut the keys into runs so that the GPU is filled; each run at least 64 keys
       const int span = s.window > 0 ? std::min(sp.max_len, s.window + qpi) : sp.max_len;
       int splits = 1;
-      if (it.second * cdiv(pairs, nw) < e->sm_count) splits = std::max(1, std::min(cdiv(span, 64), cdiv(2 * e->sm_count, it.second * cdiv(pairs, nw))));
+      if (it.second * cdiv(pairs, nw) < e->sm_count)
+        splits = std::max(1, std::min(std::min(32, cdiv(span, 64)), cdiv(2 * e->sm_count, it.second * cdiv(pairs, nw))));
       const int chunk = cdiv(cdiv(span, splits), 32) * 32;
       splits = cdiv(span, chunk);
       if (splits > 1) {
@@ -538,7 +542,7 @@ static int attention_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
       CK(cudaGetLastError());
       e->launches++;
       if (splits > 1) {
-        latent_attention_combine_kernel<T><<<it.second, 256, 0, e->stream>>>(e->part, it.first, H, R, splits, gate, L.n_in, L.c_g, static_cast<T*>(e->olat));
+        latent_attention_combine_kernel<T><<<dim3(it.second, cdiv(pairs, 8)), 256, 0, e->stream>>>(e->part, it.first, H, R, splits, gate, L.n_in, L.c_g, static_cast<T*>(e->olat));
         CK(cudaGetLastError());
         e->launches++;
       }
@@ -580,13 +584,16 @@ static int attention_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
   return 0;
 }
 
-template <int KPT, int P>
+template <int KPT, int P, int NC>
 static int launch_delta(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
   const xotb200_lm_layer& s = L.s;
-  constexpr int CPW = 32 / P, WARPS = 4;
-  const dim3 grid(sp.n_seq * s.heads, cdiv(s.vdim, WARPS * CPW));
-  delta_rule_kernel<KPT, P><<<grid, WARPS * 32, 0, e->stream>>>(e->proj, L.n_in, L.c_r, L.c_k, L.c_v, e->wlog, e->du, e->dau, sp.seqs, s.heads, s.dim, s.vdim,
-                                                                e->state + L.state_off, e->state_floats, e->oraw);
+  constexpr int CPW = (32 / P) * NC;
+  const int warps = std::max(1, std::min(4, cdiv(s.vdim, CPW)));
+  const dim3 grid(sp.n_seq * s.heads, cdiv(s.vdim, warps * CPW));
+  const int HD = s.heads * s.dim;
+  const int vec4 = (s.dim % 4 == 0 && HD % 4 == 0 && L.n_in % 4 == 0 && L.c_r % 4 == 0 && L.c_k % 4 == 0 && L.c_v % 4 == 0) ? 1 : 0;
+  delta_rule_kernel<KPT, P, NC><<<grid, warps * 32, 0, e->stream>>>(e->proj, L.n_in, L.c_r, L.c_k, L.c_v, e->wlog, e->du, e->dau, sp.seqs, s.heads, s.dim,
+                                                                    s.vdim, e->state + L.state_off, e->state_floats, e->oraw, vec4);
   CK(cudaGetLastError());
   e->launches++;
   return 0;
@@ -606,17 +613,26 @@ static int delta_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
                                                                               s.heads, s.dim, M);
   CK(cudaGetLastError());
   e->launches++;
-  if (s.dim <= 16) TRY((launch_delta<16, 1>(e, L, sp)));
-  else if (s.dim <= 32) TRY((launch_delta<16, 2>(e, L, sp)));
-  else if (s.dim <= 64) TRY((launch_delta<16, 4>(e, L, sp)));
-  else if (s.dim <= 128) TRY((launch_delta<16, 8>(e, L, sp)));
-  else TRY((launch_delta<32, 8>(e, L, sp)));
+  // the recurrence is bound by the instructions one warp issues per token (measured: ~2.8 cycles each): key rows over 8 lanes,
+  // few columns per thread, four warps per block
+  if (s.dim <= 16) TRY((launch_delta<4, 4, 2>(e, L, sp)));
+  else if (s.dim <= 32) TRY((launch_delta<8, 4, 2>(e, L, sp)));
+  else if (s.dim <= 64) TRY((launch_delta<8, 8, 4>(e, L, sp)));
+  else if (s.dim <= 128) TRY((launch_delta<16, 8, 2>(e, L, sp)));
+  else TRY((launch_delta<32, 8, 1>(e, L, sp)));
   head_norm_gate_kernel<T><<<cdiv((long)M * s.heads, 8), 256, 0, e->stream>>>(e->oraw, at<T>(e, L.onorm), e->proj, L.n_in, L.c_g, static_cast<T*>(e->oh), s.heads,
                                                                                s.vdim, e->cfg.norm_eps, M);
   CK(cudaGetLastError());
   e->launches++;
   TRY((product<T, T, float, 0>(e, static_cast<T*>(e->oh), HD, 0, at<T>(e, L.wo), HD, 1, 0, e->y, D, 0, M, D, HD, 1)));
   return 0;
+}
+
+// threads of a row's norm block: about one warp per 256 elements, at least one warp per part while parts <= 32, at most 1024
+static int norm_threads(int D, int G) {
+  int nw = std::max(1, std::min(32, D / 256));
+  if (G <= 32) nw = std::max(nw, G) / G * G;
+  return std::min(32, std::max(1, nw)) * 32;
 }
 
 template <typename T>
@@ -629,7 +645,7 @@ static int run_layers(xotb200_lm* e, const StepPlan& sp, int n_want) {
   // x += groupnorm(pending sublayer output) * its post-norm weight;  h = groupnorm(x) * w_pre  (either half may be absent)
   auto open = [&](const T* w_pre) -> int {
     if (!pend_y && !w_pre) return 0;
-    residual_groupnorm_kernel<T><<<M, 128, 0, e->stream>>>(e->x, pend_y, pend_w, w_pre, w_pre ? h : nullptr, nullptr, D, G, eps);
+    residual_groupnorm_kernel<T><<<M, norm_threads(D, G), 0, e->stream>>>(e->x, pend_y, pend_w, w_pre, w_pre ? h : nullptr, nullptr, D, G, eps);
     CK(cudaGetLastError());
     e->launches++;
     pend_y = nullptr;
@@ -664,7 +680,7 @@ static int run_layers(xotb200_lm* e, const StepPlan& sp, int n_want) {
   if (e->trace) e->trace_floats = e->layers.size() * (size_t)M * D;
   if (e->last && n_want > 0) {
     T* hw = static_cast<T*>(e->hw);
-    residual_groupnorm_kernel<T><<<n_want, 128, 0, e->stream>>>(e->x, nullptr, nullptr, at<T>(e, e->final_norm), hw, sp.want, D, G, eps);
+    residual_groupnorm_kernel<T><<<n_want, norm_threads(D, G), 0, e->stream>>>(e->x, nullptr, nullptr, at<T>(e, e->final_norm), hw, sp.want, D, G, eps);
     CK(cudaGetLastError());
     e->launches++;
     TRY((product<T, T, float, 0>(e, hw, D, 0, at<T>(e, e->head), D, 1, 0, e->logits, e->cfg.vocab, 0, n_want, e->cfg.vocab, D, 1)));

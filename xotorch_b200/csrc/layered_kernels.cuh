@@ -59,8 +59,7 @@ __global__ void embed_rows_kernel(const T* __restrict__ embed, const int* __rest
 
 // ---------------------------------------------------------------------------------------------------------------------------
 // Fused "close one sublayer, open the next":   x += groupnorm(y) * w_post ;  h = groupnorm(x) * w_pre
-// groupnorm: the row is cut into G equal consecutive parts, each divided by sqrt(mean(part^2) + eps).  One warp per part, so both
-// norms and the residual sum need no block-wide exchange.  y / w_post may be NULL (first sublayer), h / w_pre may be NULL (no
+// groupnorm: the row is cut into G equal consecutive parts, each divided by sqrt(mean(part^2) + eps).  A part is shared by a few warps of the row's block.  y / w_post may be NULL (first sublayer), h / w_pre may be NULL (no
 // sublayer follows).  src_rows (may be NULL) gathers: output row m reads x row src_rows[m] and does not write x (used for the
 // final norm on the rows whose logits are wanted).
 // ---------------------------------------------------------------------------------------------------------------------------
@@ -68,32 +67,54 @@ template <typename T>
 __global__ void residual_groupnorm_kernel(float* __restrict__ x, const float* __restrict__ y, const T* __restrict__ w_post,
                                           const T* __restrict__ w_pre, T* __restrict__ h, const int* __restrict__ src_rows, int D, int G,
                                           float eps) {
+  // `wpg` warps share one part (each a slice of it); their sums of squares meet in shared memory.  All warps walk the same
+  // number of rounds, so the barriers are uniform.
+  __shared__ float red[2][32];
   const int m = blockIdx.x;
   const int xm = src_rows ? src_rows[m] : m;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
   const int Dg = D / G;
-  for (int g = warp; g < G; g += nw) {
-    float* xr = x + (size_t)xm * D + (size_t)g * Dg;
+  const int wpg = max(1, nw / G), gpr = nw / wpg;    // warps per part, parts per round
+  const int sub = warp % wpg, gsel = warp / wpg;
+  const int sl = (Dg + wpg - 1) / wpg, d0 = sub * sl, d1 = min(Dg, d0 + sl);
+  for (int g0 = 0; g0 < G; g0 += gpr) {
+    const int g = g0 + gsel;
+    const bool on = gsel < gpr && g < G;
+    float* xr = x + (size_t)xm * D + (size_t)(on ? g : 0) * Dg;
+    const float* yr = y ? y + (size_t)m * D + (size_t)(on ? g : 0) * Dg : nullptr;
     float ry = 0.f;
     if (y) {
-      const float* yr = y + (size_t)m * D + (size_t)g * Dg;
       float s = 0.f;
-      for (int d = lane; d < Dg; d += 32) { const float v = yr[d]; s = fmaf(v, v, s); }
-      ry = 1.0f / sqrtf(warp_sum(s) / (float)Dg + eps);
+      if (on)
+        for (int d = d0 + lane; d < d1; d += 32) { const float v = yr[d]; s = fmaf(v, v, s); }
+      s = warp_sum(s);
+      if (lane == 0) red[0][warp] = s;
+      __syncthreads();
+      float t = 0.f;
+      for (int k = 0; k < wpg; ++k) t += red[0][(warp / wpg) * wpg + k];
+      ry = 1.0f / sqrtf(t / (float)Dg + eps);
     }
     float s2 = 0.f;
-    for (int d = lane; d < Dg; d += 32) {
-      float v = xr[d];
-      if (y) {
-        v += y[(size_t)m * D + (size_t)g * Dg + d] * ry * ldf(w_post + (size_t)g * Dg + d);
-        xr[d] = v;
+    if (on)
+      for (int d = d0 + lane; d < d1; d += 32) {
+        float v = xr[d];
+        if (y) {
+          v += yr[d] * ry * ldf(w_post + (size_t)g * Dg + d);
+          xr[d] = v;
+        }
+        s2 = fmaf(v, v, s2);
       }
-      s2 = fmaf(v, v, s2);
-    }
     if (h) {
-      const float rx = 1.0f / sqrtf(warp_sum(s2) / (float)Dg + eps);
-      for (int d = lane; d < Dg; d += 32) stf(h + (size_t)m * D + (size_t)g * Dg + d, xr[d] * rx * ldf(w_pre + (size_t)g * Dg + d));
+      s2 = warp_sum(s2);
+      if (lane == 0) red[1][warp] = s2;
+      __syncthreads();
+      float t = 0.f;
+      for (int k = 0; k < wpg; ++k) t += red[1][(warp / wpg) * wpg + k];
+      const float rx = 1.0f / sqrtf(t / (float)Dg + eps);
+      if (on)
+        for (int d = d0 + lane; d < d1; d += 32) stf(h + (size_t)m * D + (size_t)g * Dg + d, xr[d] * rx * ldf(w_pre + (size_t)g * Dg + d));
     }
+    __syncthreads();                                 // `red` is reused by the next round
   }
 }
 
@@ -290,32 +311,31 @@ __global__ void latent_attention_kernel(const float* __restrict__ qfull, const T
   }
 }
 
-// merges the key runs of latent_attention_kernel: one warp per (row, head) pair of the listed items
+// merges the key runs of latent_attention_kernel: one warp per (row, head) pair of the listed items (grid.y covers the pairs);
+// lane z first turns run z's {max, sum} into its weight exp(max_z - max) (at most 32 runs), then the lanes split the R columns
 template <typename T>
 __global__ void latent_attention_combine_kernel(const float* __restrict__ part, const Item* __restrict__ items, int H, int R, int splits,
                                                 const float* __restrict__ gate, int gate_ld, int gate_col0, T* __restrict__ olat) {
   const Item it = items[blockIdx.x];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-  for (int pair = warp; pair < it.n_rows * H; pair += nw) {
-    const int m = it.row0 + pair / H, h = pair % H;
-    const float* src = part + ((size_t)m * H + h) * splits * (size_t)(2 + R);
-    float mx = -INFINITY;
-    for (int z = 0; z < splits; ++z) mx = fmaxf(mx, src[(size_t)z * (2 + R)]);
-    float den = 0.f;
+  const int pair = blockIdx.y * nw + warp;
+  if (pair >= it.n_rows * H) return;
+  const int m = it.row0 + pair / H, h = pair % H;
+  const float* src = part + ((size_t)m * H + h) * splits * (size_t)(2 + R);
+  const float mz = lane < splits ? src[(size_t)lane * (2 + R)] : -INFINITY;
+  const float mx = warp_max(mz);
+  const float wz = mz == -INFINITY ? 0.f : expf(mz - mx);
+  const float den = warp_sum(lane < splits ? src[(size_t)lane * (2 + R) + 1] * wz : 0.f);
+  float g = 1.0f / den;
+  if (gate) g *= sigmoidf_(gate[(size_t)m * gate_ld + gate_col0 + h]);
+  for (int d0 = 0; d0 < R; d0 += 32) {
+    const int d = d0 + lane;
+    float a = 0.f;
     for (int z = 0; z < splits; ++z) {
-      const float mz = src[(size_t)z * (2 + R)];
-      if (mz != -INFINITY) den += src[(size_t)z * (2 + R) + 1] * expf(mz - mx);
+      const float w = __shfl_sync(0xffffffffu, wz, z);
+      if (w != 0.f && d < R) a = fmaf(src[(size_t)z * (2 + R) + 2 + d], w, a);
     }
-    float g = 1.0f / den;
-    if (gate) g *= sigmoidf_(gate[(size_t)m * gate_ld + gate_col0 + h]);
-    for (int d = lane; d < R; d += 32) {
-      float a = 0.f;
-      for (int z = 0; z < splits; ++z) {
-        const float mz = src[(size_t)z * (2 + R)];
-        if (mz != -INFINITY) a += src[(size_t)z * (2 + R) + 2 + d] * expf(mz - mx);
-      }
-      stf(olat + ((size_t)m * H + h) * R + d, a * g);
-    }
+    if (d < R) stf(olat + ((size_t)m * H + h) * R + d, a * g);
   }
 }
 
@@ -356,34 +376,42 @@ __global__ void delta_prepare_kernel(const float* __restrict__ proj, int ld, int
 __device__ __forceinline__ void cp_async4(float* dst_smem, const float* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst_smem)), "l"(src) : "memory");
 }
+__device__ __forceinline__ void cp_async16(float* dst_smem, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst_smem)), "l"(src) : "memory");
+}
 
-template <int KPT, int P>
+// A thread owns NC value columns x KPT key rows of the state (row i = e * P + part), so the token's vectors, read from shared
+// memory once, serve NC columns and the NC recurrences run as independent chains.  vec4: every source row is 16-byte aligned
+// (sizes and offsets multiples of 4 floats), so the staging uses 16-byte cp.async.
+template <int KPT, int P, int NC>
 __global__ void delta_rule_kernel(const float* __restrict__ proj, int ld, int col_r, int col_k, int col_v, const float* __restrict__ wdec,
                                   const float* __restrict__ uvec, const float* __restrict__ auvec, const Item* __restrict__ seqs, int H, int dk,
-                                  int dv, float* __restrict__ state, size_t state_slot_stride, float* __restrict__ o_raw) {
+                                  int dv, float* __restrict__ state, size_t state_slot_stride, float* __restrict__ o_raw, int vec4) {
   constexpr int DKP = KPT * P;                       // padded key size (>= dk, and >= dv: the design uses one size for both)
   constexpr int CH = DKP <= 64 ? 16 : DKP <= 128 ? 8 : 4;   // tokens per buffer: two buffers fill the 48 KB of static shared memory
-  __shared__ float buf[2][CH][6][DKP];               // per token: w, a*u, u, k, r, v
+  __shared__ __align__(16) float buf[2][CH][6][DKP]; // per token: w, a*u, u, k, r, v
   const Item sq = seqs[blockIdx.x / H];
   const int h = blockIdx.x % H;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  constexpr int CPW = 32 / P;                        // columns per warp
-  const int col = (blockIdx.y * (blockDim.x >> 5) + warp) * CPW + lane / P, part = lane % P;   // grid.y splits the value columns
-  const bool col_ok = col < dv;
+  constexpr int CPW = (32 / P) * NC;                 // columns per warp
+  const int col0 = (blockIdx.y * (blockDim.x >> 5) + warp) * CPW + (lane / P) * NC, part = lane % P;   // grid.y splits the value columns
   float* S = state + (size_t)sq.slot * state_slot_stride + (size_t)h * dk * dv;
-  float s[KPT];
+  float s[KPT][NC];
 #pragma unroll
-  for (int e = 0; e < KPT; ++e) {
-    const int i = e * P + part;
-    s[e] = (col_ok && i < dk) ? S[(size_t)i * dv + col] : 0.f;
-  }
+  for (int e = 0; e < KPT; ++e)
+#pragma unroll
+    for (int c = 0; c < NC; ++c) {
+      const int i = e * P + part;
+      s[e][c] = (col0 + c < dv && i < dk) ? S[(size_t)i * dv + col0 + c] : 0.f;
+    }
   for (int e = threadIdx.x; e < 2 * CH * 6 * DKP; e += blockDim.x) (&buf[0][0][0][0])[e] = 0.f;   // the padding stays zero
   __syncthreads();
   const int HD = H * dk;
   auto issue = [&](int c) {
     const int t0 = c * CH, nt = min(CH, sq.n_rows - t0);
-    for (int e = threadIdx.x; e < nt * 6 * dk; e += blockDim.x) {
-      const int t = e / (6 * dk), rem = e % (6 * dk), vec = rem / dk, i = rem % dk;
+    const int per = vec4 ? dk / 4 : dk;              // copies per vector
+    for (int e = threadIdx.x; e < nt * 6 * per; e += blockDim.x) {
+      const int t = e / (6 * per), rem = e % (6 * per), vec = rem / per, i = (rem % per) * (vec4 ? 4 : 1);
       const size_t m = (size_t)sq.row0 + t0 + t;
       const float* src = vec == 0 ? wdec + m * HD + h * dk + i
                        : vec == 1 ? auvec + m * HD + h * dk + i
@@ -391,7 +419,8 @@ __global__ void delta_rule_kernel(const float* __restrict__ proj, int ld, int co
                        : vec == 3 ? proj + m * ld + col_k + h * dk + i
                        : vec == 4 ? proj + m * ld + col_r + h * dk + i
                                   : proj + m * ld + col_v + h * dv + i;
-      cp_async4(&buf[c & 1][t][vec][i], src);
+      if (vec4) cp_async16(&buf[c & 1][t][vec][i], src);
+      else cp_async4(&buf[c & 1][t][vec][i], src);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
@@ -408,30 +437,49 @@ __global__ void delta_rule_kernel(const float* __restrict__ proj, int ld, int co
     const int nt = min(CH, sq.n_rows - c * CH);
     float(*b)[6][DKP] = buf[c & 1];
     for (int t = 0; t < nt; ++t) {
-      float dot = 0.f;
+      float dot[NC], out[NC], vj[NC];
 #pragma unroll
-      for (int e = 0; e < KPT; ++e) dot = fmaf(b[t][2][e * P + part], s[e], dot);
+      for (int x = 0; x < NC; ++x) { dot[x] = 0.f; out[x] = 0.f; vj[x] = col0 + x < DKP ? b[t][5][col0 + x] : 0.f; }
 #pragma unroll
-      for (int o = P / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-      const float vj = col_ok ? b[t][5][col] : 0.f;
-      float out = 0.f;
+      for (int e = 0; e < KPT; ++e) {
+        const float u = b[t][2][e * P + part];
+#pragma unroll
+        for (int x = 0; x < NC; ++x) dot[x] = fmaf(u, s[e][x], dot[x]);
+      }
+#pragma unroll
+      for (int o = P / 2; o > 0; o >>= 1)
+#pragma unroll
+        for (int x = 0; x < NC; ++x) dot[x] += __shfl_xor_sync(0xffffffffu, dot[x], o);
 #pragma unroll
       for (int e = 0; e < KPT; ++e) {
         const int i = e * P + part;
-        s[e] = fmaf(b[t][0][i], s[e], fmaf(-b[t][1][i], dot, b[t][3][i] * vj));
-        out = fmaf(s[e], b[t][4][i], out);
+        const float w = b[t][0][i], au = b[t][1][i], kk = b[t][3][i], rr = b[t][4][i];
+#pragma unroll
+        for (int x = 0; x < NC; ++x) {
+          s[e][x] = fmaf(w, s[e][x], fmaf(-au, dot[x], kk * vj[x]));
+          out[x] = fmaf(s[e][x], rr, out[x]);
+        }
       }
 #pragma unroll
-      for (int o = P / 2; o > 0; o >>= 1) out += __shfl_xor_sync(0xffffffffu, out, o);
-      if (col_ok && part == 0) o_raw[((size_t)sq.row0 + c * CH + t) * (size_t)(H * dv) + h * dv + col] = out;
+      for (int o = P / 2; o > 0; o >>= 1)
+#pragma unroll
+        for (int x = 0; x < NC; ++x) out[x] += __shfl_xor_sync(0xffffffffu, out[x], o);
+      if (part == 0) {
+        float* dst = o_raw + ((size_t)sq.row0 + c * CH + t) * (size_t)(H * dv) + h * dv + col0;
+#pragma unroll
+        for (int x = 0; x < NC; ++x)
+          if (col0 + x < dv) dst[x] = out[x];
+      }
     }
     __syncthreads();                                 // the buffer is refilled two chunks later
   }
 #pragma unroll
-  for (int e = 0; e < KPT; ++e) {
-    const int i = e * P + part;
-    if (col_ok && i < dk) S[(size_t)i * dv + col] = s[e];
-  }
+  for (int e = 0; e < KPT; ++e)
+#pragma unroll
+    for (int c = 0; c < NC; ++c) {
+      const int i = e * P + part;
+      if (col0 + c < dv && i < dk) S[(size_t)i * dv + col0 + c] = s[e][c];
+    }
 }
 
 // Output side of the delta-rule mixer: per (row, head) o / rms(o) * w_norm * sigmoid(gate) -> T, the operand of the output product.
