@@ -421,3 +421,21 @@ def test_graph_replay_of_decode_steps_changes_nothing(dtype):
   ref = oracle_logits(cfg, W, seqs[0][:280])[0]
   got = np.stack([x[0] for x in replayed])
   assert row_err(got, ref[240:280]) < TOL[dtype]
+
+
+def test_command_line_generates_from_a_model_directory(tmp_path, capsys):
+  """`xotorch_b200.cli generate` on a layered model directory: registry -> loader -> batch scheduler -> greedy ids"""
+  import json
+  from xotorch_b200.cli import main
+  cfg = config(MIXED)
+  W = zo.random_weights(cfg, 8)
+  write_model_dir(tmp_path, cfg, W)
+  prompts = [rand_tokens(cfg["vocab"], 6, 1), rand_tokens(cfg["vocab"], 11, 2)]
+  arg = ";".join(",".join(str(int(t)) for t in p) for p in prompts)
+  assert main(["generate", "--model", str(tmp_path), "--prompt-ids", arg, "--max-tokens", "5", "--dtype", "float32"]) == 0
+  lines = [json.loads(l) for l in capsys.readouterr().out.strip().splitlines()]
+  for p, line in zip(prompts, lines):
+    ids, gaps = oracle_greedy(cfg, W, p, 5)
+    if line["ids"] != ids:
+      d = next(i for i in range(5) if line["ids"][i] != ids[i])
+      assert gaps[d] < 1e-3
