@@ -563,17 +563,25 @@ static int attention_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
       TRY((product<bf16, bf16, bf16, 0>(e, cbuf, R + dr, 0, at<bf16>(e, L.uk_rows), R, 1, 0, knx, (long)H * dn, 0, fl->n_keys, H * dn, R, 1)));
       TRY((product<bf16, bf16, bf16, 0>(e, cbuf, R + dr, 0, at<bf16>(e, L.uv), R, 1, 0, vxx, (long)H * dv, 0, fl->n_keys, H * dv, R, 1)));
       const int dqp = (dn + dr + 15) & ~15, dvt = dv <= 64 ? 8 : 16;
-      const size_t smem = ((size_t)2 * 64 * (dqp + 8) + (size_t)8 * dvt * 72) * 2;
       const dim3 grid(fl->n_tiles, H);
-      if (dvt == 8) {
-        auto kern = latent_flash_kernel<8>;
-        TRY(opt_in_smem(kern, smem));
-        kern<<<grid, 128, smem, e->stream>>>(q16, knx, cbuf, vxx, fl->tiles, H, dn, dr, dv, R, s.scale, s.window, gate, L.n_in, L.c_g, static_cast<bf16*>(e->oh));
+      const bool aligned = dn % 8 == 0 && dr % 8 == 0 && R % 8 == 0 && dv % 8 == 0;
+#define LAUNCH_FLASH(KERN, SMEM)                                                                                                                  \
+  do {                                                                                                                                            \
+    auto kern = KERN;                                                                                                                             \
+    TRY(opt_in_smem(kern, SMEM));                                                                                                                 \
+    kern<<<grid, 128, SMEM, e->stream>>>(q16, knx, cbuf, vxx, fl->tiles, H, dn, dr, dv, R, s.scale, s.window, gate, L.n_in, L.c_g,               \
+                                         static_cast<bf16*>(e->oh));                                                                              \
+  } while (0)
+      if (aligned) {   // whole 16-byte chunks: cp.async double buffering, ldmatrix fragments
+        const size_t smem = ((size_t)3 * 64 * (dqp + 8) + (size_t)2 * 64 * (8 * dvt + 8)) * 2;
+        if (dvt == 8) LAUNCH_FLASH(latent_flash_aligned_kernel<8>, smem);
+        else LAUNCH_FLASH(latent_flash_aligned_kernel<16>, smem);
       } else {
-        auto kern = latent_flash_kernel<16>;
-        TRY(opt_in_smem(kern, smem));
-        kern<<<grid, 128, smem, e->stream>>>(q16, knx, cbuf, vxx, fl->tiles, H, dn, dr, dv, R, s.scale, s.window, gate, L.n_in, L.c_g, static_cast<bf16*>(e->oh));
+        const size_t smem = ((size_t)2 * 64 * (dqp + 8) + (size_t)8 * dvt * 72) * 2;
+        if (dvt == 8) LAUNCH_FLASH(latent_flash_kernel<8>, smem);
+        else LAUNCH_FLASH(latent_flash_kernel<16>, smem);
       }
+#undef LAUNCH_FLASH
       CK(cudaGetLastError());
       e->launches++;
       e->flash_launches++;

@@ -950,4 +950,171 @@ latent_flash_kernel(const bf16* __restrict__ q16, const bf16* __restrict__ kn, c
   }
 }
 
+// The same attention for sizes whose rows are whole 16-byte chunks (dn, dr, R, dv multiples of 8): K and V tiles arrive by 16-byte
+// cp.async into two buffers each (the next tile is in flight while this one is multiplied), V stays in its natural [key][column]
+// layout and is transposed on the way into registers by ldmatrix.trans; Q and K fragments come from ldmatrix too.
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const bf16* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((uint32_t)__cvta_generic_to_shared(p)));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const bf16* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((uint32_t)__cvta_generic_to_shared(p)));
+}
+__device__ __forceinline__ void cp_async16_b(bf16* dst_smem, const bf16* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst_smem)), "l"(src) : "memory");
+}
+
+template <int DVT>
+__global__ void __launch_bounds__(128)
+latent_flash_aligned_kernel(const bf16* __restrict__ q16, const bf16* __restrict__ kn, const bf16* __restrict__ cbuf, const bf16* __restrict__ vx,
+                            const FlashTile* __restrict__ tiles, int H, int dn, int dr, int dv, int R, float scale, int window,
+                            const float* __restrict__ gate, int gate_ld, int gate_col0, bf16* __restrict__ out) {
+  extern __shared__ __align__(16) uint8_t fsm[];
+  const FlashTile tl = tiles[blockIdx.x];
+  const int h = blockIdx.y;
+  const int DQ = dn + dr, DQP = (DQ + 15) & ~15, QS = DQP + 8;
+  constexpr int VS = 8 * DVT + 8;
+  bf16* Qs = reinterpret_cast<bf16*>(fsm);          // [64][QS]
+  bf16* Ks = Qs + 64 * QS;                          // [2][64][QS]
+  bf16* Vs = Ks + 2 * 64 * QS;                      // [2][64][VS]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const uint4 zero4 = make_uint4(0, 0, 0, 0);
+  const int last = tl.pos0 + tl.n_rows - 1;
+  const int first = window > 0 ? max(0, tl.pos0 - window + 1) : 0;
+  const int qc = DQP / 8;
+
+  auto issue = [&](int j0, int bsel) {
+    bf16* kd = Ks + bsel * 64 * QS;
+    for (int e = threadIdx.x; e < 64 * qc; e += 128) {
+      const int r = e / qc, c = (e % qc) * 8, j = j0 + r;
+      bf16* dst = kd + r * QS + c;
+      const size_t idx = (size_t)(tl.kbase + (j - tl.kfirst));
+      if (j > last || c >= DQ) *reinterpret_cast<uint4*>(dst) = zero4;
+      else if (c < dn) cp_async16_b(dst, kn + idx * ((size_t)H * dn) + (size_t)h * dn + c);
+      else cp_async16_b(dst, cbuf + idx * (size_t)(R + dr) + R + (c - dn));
+    }
+    bf16* vd = Vs + bsel * 64 * VS;
+    for (int e = threadIdx.x; e < 64 * DVT; e += 128) {
+      const int r = e / DVT, c = (e % DVT) * 8, j = j0 + r;
+      bf16* dst = vd + r * VS + c;
+      if (j > last || c >= dv) *reinterpret_cast<uint4*>(dst) = zero4;
+      else cp_async16_b(dst, vx + (size_t)(tl.kbase + (j - tl.kfirst)) * ((size_t)H * dv) + (size_t)h * dv + c);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  // Q tile (plain 16-byte copies; rows beyond n_rows and the padding are zero)
+  for (int e = threadIdx.x; e < 64 * qc; e += 128) {
+    const int r = e / qc, c = (e % qc) * 8;
+    uint4 v = zero4;
+    if (r < tl.n_rows && c < DQ) v = *reinterpret_cast<const uint4*>(q16 + ((size_t)(tl.row0 + r) * H + h) * DQ + c);
+    *reinterpret_cast<uint4*>(Qs + r * QS + c) = v;
+  }
+  float o[DVT][4];
+#pragma unroll
+  for (int i = 0; i < DVT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float mx[2] = {-INFINITY, -INFINITY}, den[2] = {0.f, 0.f};
+  const int pos_lo = tl.pos0 + warp * 16 + g, pos_hi = pos_lo + 8;
+  const int ntile = (last - first) / 64 + 1;
+  issue(first, 0);
+  for (int it = 0; it < ntile; ++it) {
+    const int j0 = first + it * 64, bsel = it & 1;
+    if (it + 1 < ntile) {
+      issue(j0 + 64, bsel ^ 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    const bf16* kt = Ks + bsel * 64 * QS;
+    const bf16* vt = Vs + bsel * 64 * VS;
+    float s[8][4];
+#pragma unroll
+    for (int n = 0; n < 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+    for (int k0 = 0; k0 < DQP; k0 += 16) {
+      uint32_t a[4];
+      ldsm_x4(a, Qs + (warp * 16 + (lane & 15)) * QS + k0 + (lane >> 4) * 8);
+#pragma unroll
+      for (int n = 0; n < 8; n += 2) {
+        uint32_t b[4];
+        ldsm_x4(b, kt + (n * 8 + (lane & 7) + ((lane >> 4) << 3)) * QS + k0 + ((lane >> 3) & 1) * 8);
+        mma_bf16_16816(s[n], a[0], a[1], a[2], a[3], b[0], b[1]);
+        mma_bf16_16816(s[n + 1], a[0], a[1], a[2], a[3], b[2], b[3]);
+      }
+    }
+    float tmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int n = 0; n < 8; ++n)
+#pragma unroll
+      for (int x = 0; x < 4; ++x) {
+        const int j = j0 + n * 8 + 2 * t + (x & 1), pos = (x < 2) ? pos_lo : pos_hi;
+        const bool vis = j <= pos && j <= last && (window == 0 || pos - j < window);
+        s[n][x] = vis ? s[n][x] * scale : -INFINITY;
+        tmax[x >> 1] = fmaxf(tmax[x >> 1], s[n][x]);
+      }
+    float corr[2], nmx[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 1));
+      tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 2));
+      nmx[r] = fmaxf(mx[r], tmax[r]);
+      corr[r] = (mx[r] == -INFINITY) ? 0.f : expf(mx[r] - nmx[r]);
+      mx[r] = nmx[r];
+    }
+    float psum[2] = {0.f, 0.f};
+#pragma unroll
+    for (int n = 0; n < 8; ++n)
+#pragma unroll
+      for (int x = 0; x < 4; ++x) {
+        const float p = (s[n][x] == -INFINITY) ? 0.f : expf(s[n][x] - nmx[x >> 1]);
+        s[n][x] = p;
+        psum[x >> 1] += p;
+      }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      psum[r] += __shfl_xor_sync(0xffffffffu, psum[r], 1);
+      psum[r] += __shfl_xor_sync(0xffffffffu, psum[r], 2);
+      den[r] = den[r] * corr[r] + psum[r];
+    }
+#pragma unroll
+    for (int i = 0; i < DVT; ++i) { o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1]; }
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {
+      uint32_t ah[4], al[4];
+#pragma unroll
+      for (int x = 0; x < 4; ++x) {
+        const float p0 = s[2 * kk + (x >> 1)][(x & 1) * 2], p1 = s[2 * kk + (x >> 1)][(x & 1) * 2 + 1];
+        const float h0 = __bfloat162float(__float2bfloat16_rn(p0)), h1 = __bfloat162float(__float2bfloat16_rn(p1));
+        ah[x] = pack_bf16x2(h0, h1);
+        al[x] = pack_bf16x2(p0 - h0, p1 - h1);
+      }
+#pragma unroll
+      for (int i = 0; i < DVT; i += 2) {
+        uint32_t b[4];
+        ldsm_x4_trans(b, vt + (kk * 16 + (lane & 15)) * VS + i * 8 + (lane >> 4) * 8);
+        mma_bf16_16816(o[i], ah[0], ah[1], ah[2], ah[3], b[0], b[1]);
+        mma_bf16_16816(o[i], al[0], al[1], al[2], al[3], b[0], b[1]);
+        mma_bf16_16816(o[i + 1], ah[0], ah[1], ah[2], ah[3], b[2], b[3]);
+        mma_bf16_16816(o[i + 1], al[0], al[1], al[2], al[3], b[2], b[3]);
+      }
+    }
+    __syncthreads();                                 // this buffer is refilled by the next iteration's issue
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int qi = warp * 16 + g + r * 8;
+    if (qi >= tl.n_rows) continue;
+    const int m = tl.row0 + qi;
+    float sc = 1.0f / den[r];
+    if (gate) sc *= sigmoidf_(gate[(size_t)m * gate_ld + gate_col0 + h]);
+    bf16* dst = out + (size_t)m * ((size_t)H * dv) + (size_t)h * dv;
+#pragma unroll
+    for (int i = 0; i < DVT; ++i) {
+      const int c = i * 8 + 2 * t;
+      if (c < dv) *reinterpret_cast<uint32_t*>(dst + c) = pack_bf16x2(o[i][r * 2] * sc, o[i][r * 2 + 1] * sc);
+    }
+  }
+}
+
 }  // namespace xl
