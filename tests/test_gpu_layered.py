@@ -439,3 +439,13 @@ def test_command_line_generates_from_a_model_directory(tmp_path, capsys):
     if line["ids"] != ids:
       d = next(i for i in range(5) if line["ids"][i] != ids[i])
       assert gaps[d] < 1e-3
+
+
+def test_wide_values_keep_all_attention_on_the_absorbed_kernel():
+  """a value size beyond what the expanded kernel's tiles hold: prompts of any length still come out right (absorbed form)"""
+  cfg = config([attn("latent_attention", heads=2, dim=8, rot_dim=8, vdim=136, kv_rank=16, q_rank=8, ff=0)], width=32, groups=2)
+  W = zo.random_weights(cfg, 23)
+  n = make_engine(cfg, W, "bfloat16")
+  check(n, cfg, W, rand_tokens(cfg["vocab"], 70, 2), [40, 30], "bfloat16")
+  assert n.prompt_attention_launches() == 0
+  n.close()

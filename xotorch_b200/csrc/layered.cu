@@ -137,6 +137,7 @@ struct xotb200_lm {
   bool graphs_on = true;                               // decode steps are replayed from CUDA graphs
   std::map<std::array<long, 5>, GraphSlot> graphs;
   int64_t graph_replays = 0;
+  bool flash_fits = true;                              // every attention layer fits the expanded kernel's tile sizes
   bool flash_on = true;                                // bf16: prompt portions of FLASH_MIN_ROWS rows or more use the expanded tensor-core attention
   std::vector<int> stage_build;
   int64_t launches = 0, tc_launches = 0, flash_launches = 0;
@@ -169,6 +170,7 @@ static int build_layout(xotb200_lm* e, const xotb200_lm_layer* all) {
       const int H = s.heads, dn = s.dim, dr = s.rot_dim, dv = s.vdim, R = s.kv_rank, HQ = H * (dn + dr);
       REQUIRE(R >= 1 && R <= 512, "layer %d: kv_rank %d outside 1..512", li, R);
       REQUIRE(dv >= 1 && dr >= 0 && s.rot_dims <= dr && s.rot_dims % 2 == 0 && s.rot_dims >= 0, "layer %d: bad rotation sizes", li);
+      REQUIRE(s.rot_layout == XOTB200_LM_ROT_INTERLEAVED || s.rot_layout == XOTB200_LM_ROT_HALF, "layer %d: unknown rotation layout %d", li, s.rot_layout);
       REQUIRE(s.window >= 0, "layer %d: negative window", li);
       const int nq = s.q_rank > 0 ? s.q_rank : HQ;
       L.c_q = 0; L.c_kv = nq; L.c_g = nq + R + dr;
@@ -196,6 +198,9 @@ static int build_layout(xotb200_lm* e, const xotb200_lm_layer* all) {
       e->max_olat = std::max(e->max_olat, H * R);
       e->max_oh = std::max(e->max_oh, H * dv);
       e->max_w = std::max(e->max_w, R + dr);
+      // the expanded prompt attention holds dv <= 128 value columns per warp row and 256 query/key entries per tile row; a model with
+      // a wider layer keeps ALL its attention on the absorbed kernel (the split into few-row and many-row requests is per step)
+      if (dv > 128 || ((dn + dr + 15) & ~15) > 256) e->flash_fits = false;
     } else if (s.mixer == XOTB200_LM_MIX_DELTA_RULE) {
       const int HD = s.heads * s.dim;
       REQUIRE(s.vdim == s.dim, "layer %d: the delta rule uses one size for keys and values", li);
@@ -497,8 +502,7 @@ static int attention_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
   const StepPlan::Flash* fl = nullptr;
   if constexpr (std::is_same<T, bf16>::value) {
     auto f = sp.flash.find(s.window);
-    const int dqp = (dn + dr + 15) & ~15;
-    if (f != sp.flash.end() && f->second.n_tiles > 0 && dv <= 128 && dqp <= 256) fl = &f->second;
+    if (f != sp.flash.end() && f->second.n_tiles > 0) fl = &f->second;
   }
   const float* gate = s.out_gate ? e->proj : nullptr;
   if (sp.any_short || !fl) {
@@ -515,11 +519,11 @@ static int attention_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
     if (it.second > 0) {
       const int pairs = qpi * H, nw = std::min(R > 256 ? 16 : 32, pairs);   // the widest accumulator variant needs 70 registers: 16 warps at most
       const size_t smem = ((size_t)32 * ((R + dr) | 1) + (size_t)nw * (R + dr)) * 4;
-      // few work items (decoding): cut the keys into runs so that the GPU is filled; each run at least 64 keys
+      // few work items (decoding): cut the keys into runs so that the GPU is filled; each run at least one 32-key tile
       const int span = s.window > 0 ? std::min(sp.max_len, s.window + qpi) : sp.max_len;
       int splits = 1;
       if (it.second * cdiv(pairs, nw) < e->sm_count)
-        splits = std::max(1, std::min(std::min(32, cdiv(span, 64)), cdiv(2 * e->sm_count, it.second * cdiv(pairs, nw))));
+        splits = std::max(1, std::min(std::min(32, cdiv(span, 32)), cdiv(2 * e->sm_count, it.second * cdiv(pairs, nw))));
       const int chunk = cdiv(cdiv(span, splits), 32) * 32;
       splits = cdiv(span, chunk);
       if (splits > 1) {
@@ -993,7 +997,7 @@ int xotb200_lm_step(xotb200_lm* e, int n_seq, const int32_t* slots, const int32_
     for (long m = 0; m < M; ++m) REQUIRE(tokens[m] >= 0 && tokens[m] < V, "token id %d outside the vocabulary of %d", tokens[m], V);
   TRY(ensure_scratch(e, (int)M, n_want));
   // ---- commit: pages and lengths; the step's index arrays are built in one host vector and copied once
-  const bool use_flash = e->esz == 2 && e->flash_on;
+  const bool use_flash = e->esz == 2 && e->flash_on && e->flash_fits;
   std::vector<int> qpis, windows;
   for (auto& L : e->layers)
     if (L.s.mixer == XOTB200_LM_MIX_LATENT_ATTN) {

@@ -601,21 +601,29 @@ gemv_rows_kernel(const TA* __restrict__ A, long lda, long a_batch, const TB* __r
 #pragma unroll
       for (int m = 0; m < MR; ++m) acc[r][m] = 0.f;
     if (vec_ok) {
-      for (int k = kbeg + lane * VEC; k < kend; k += 32 * VEC) {
-        uint4 raw[RB];
+      // two steps of the slice at a time: 2 x RB independent 16-byte loads per lane are in flight before the first FMA
+      for (int k = kbeg + lane * VEC; k < kend; k += 64 * VEC) {
+        uint4 raw[2][RB];
 #pragma unroll
-        for (int r = 0; r < RB; ++r)
-          raw[r] = n0 + r < N ? *reinterpret_cast<const uint4*>(B + (size_t)(n0 + r) * sbn + k) : make_uint4(0, 0, 0, 0);
+        for (int u = 0; u < 2; ++u)
 #pragma unroll
-        for (int v = 0; v < VEC; ++v) {
-          float av[MR];
+          for (int r = 0; r < RB; ++r)
+            raw[u][r] = (n0 + r < N && k + u * 32 * VEC < kend) ? *reinterpret_cast<const uint4*>(B + (size_t)(n0 + r) * sbn + k + u * 32 * VEC)
+                                                                : make_uint4(0, 0, 0, 0);
 #pragma unroll
-          for (int m = 0; m < MR; ++m) av[m] = m < M ? a_s[m * K + k + v] : 0.f;
+        for (int u = 0; u < 2; ++u) {
+          const int ku = min(k + u * 32 * VEC, K - VEC);     // past the slice the weights read as zero; the index stays inside a_s
 #pragma unroll
-          for (int r = 0; r < RB; ++r) {
-            const float w = ldf(reinterpret_cast<const TB*>(&raw[r]) + v);
+          for (int v = 0; v < VEC; ++v) {
+            float av[MR];
 #pragma unroll
-            for (int m = 0; m < MR; ++m) acc[r][m] = fmaf(av[m], w, acc[r][m]);
+            for (int m = 0; m < MR; ++m) av[m] = m < M ? a_s[m * K + ku + v] : 0.f;
+#pragma unroll
+            for (int r = 0; r < RB; ++r) {
+              const float w = ldf(reinterpret_cast<const TB*>(&raw[u][r]) + v);
+#pragma unroll
+              for (int m = 0; m < MR; ++m) acc[r][m] = fmaf(av[m], w, acc[r][m]);
+            }
           }
         }
       }

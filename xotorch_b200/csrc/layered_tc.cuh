@@ -111,6 +111,7 @@ ltc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       xb::tc_fence_after();
       TC* crow = static_cast<TC*>(a.C) + (size_t)z * a.c_batch + (size_t)row * a.ldc;
       const bool vec = (sizeof(TC) == 4) && ((a.ldc | a.c_batch) % 4 == 0) && ((reinterpret_cast<uintptr_t>(a.C) & 15) == 0);
+      const bool vec16 = (sizeof(TC) == 2) && ((a.ldc | a.c_batch) % 8 == 0) && ((reinterpret_cast<uintptr_t>(a.C) & 15) == 0);
 #pragma unroll 1
       for (int c0 = 0; c0 < NT; c0 += 16) {
         uint32_t v[16];
@@ -127,6 +128,16 @@ ltc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           float4* d4 = reinterpret_cast<float4*>(reinterpret_cast<float*>(crow) + n);
 #pragma unroll
           for (int j = 0; j < 4; ++j) d4[j] = make_float4(f[4 * j], f[4 * j + 1], f[4 * j + 2], f[4 * j + 3]);
+        } else if (vec16 && n + 16 <= a.N) {
+          uint32_t pk[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            __nv_bfloat162 h2 = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+            pk[j] = *reinterpret_cast<uint32_t*>(&h2);
+          }
+          uint4* d4 = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(crow) + n);
+          d4[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          d4[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
         } else {
 #pragma unroll
           for (int j = 0; j < 16; ++j)
