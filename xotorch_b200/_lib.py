@@ -154,17 +154,22 @@ _lm_lib = None
 
 def load_lm(path: os.PathLike | None = None, build: bool = True) -> C.CDLL:
   """dlopen libxotb200_lm.so (once).  In a checkout that has not been built yet the library is compiled first — only this one
-  (`make lm`, a few seconds of nvcc), not the shard engine's persistent kernels.  Raises if it cannot be had: no CPU fallback."""
+  (`make lm`, a few seconds of nvcc), not the shard engine's persistent kernels; a library older than its sources is rebuilt
+  when the tree is writable.  Raises if it cannot be had: no CPU fallback."""
   global _lm_lib
   if _lm_lib is not None and path is None:
     return _lm_lib
   p = Path(path) if path else Path(os.environ.get("XOTB200_LM_LIB", LM_LIB_PATH))
-  if not p.exists() and build and path is None and "XOTB200_LM_LIB" not in os.environ:
-    import subprocess
+  if build and path is None and "XOTB200_LM_LIB" not in os.environ:
     src = Path(__file__).resolve().parent / "csrc"
-    r = subprocess.run(["make", "-C", str(src), "lm"], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
-    if r.returncode != 0:
-      raise ImportError(f"building {p} failed:\n{r.stdout[-4000:]}")
+    deps = [src / n for n in ("layered.cu", "layered_kernels.cuh", "layered_tc.cuh", "prefill_tc.cuh", "kernels.cuh", "st_header.h")]
+    deps.append(src.parent.parent / "include" / "xotb200_lm.h")
+    stale = p.exists() and any(d.exists() and d.stat().st_mtime > p.stat().st_mtime for d in deps)
+    if not p.exists() or stale:
+      import subprocess
+      r = subprocess.run(["make", "-C", str(src), "lm"], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+      if r.returncode != 0 and not p.exists():
+        raise ImportError(f"building {p} failed:\n{r.stdout[-4000:]}")
   if not p.exists():
     raise ImportError(f"{p} not found: build it with `make -C xotorch_b200/csrc lm` — xotorch_b200 has no CPU fallback")
   lib = C.CDLL(str(p))
