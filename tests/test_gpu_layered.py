@@ -32,6 +32,9 @@ SINGLE = {
   "latent_window_1": [attn("latent_attention_2", window=1, ff=0)],
   "latent_odd_sizes": [attn("latent_attention", heads=7, dim=5, rot_dim=6, vdim=3, kv_rank=37, q_rank=11, ff=0)],
   "latent_wide_rank": [attn("latent_attention_2", heads=2, dim=16, rot_dim=8, vdim=16, kv_rank=130, window=50, ff=0)],
+  "latent_one_head": [attn("latent_attention", heads=1, dim=12, rot_dim=4, vdim=20, kv_rank=24, q_rank=6, ff=0)],
+  "latent_rank_260": [attn("latent_attention", heads=3, dim=8, rot_dim=8, vdim=8, kv_rank=260, q_rank=16, ff=0)],
+  "latent_many_heads": [attn("latent_attention_2", heads=40, dim=4, rot_dim=4, vdim=4, kv_rank=16, window=11, ff=0)],
   "delta": [delta()],
   "delta_one_head_wide": [delta(heads=1, dim=40, decay_rank=1)],
   "delta_dim_20": [delta(heads=3, dim=20, decay_rank=5)],
@@ -54,6 +57,8 @@ def test_one_layer_models(name, dtype):
   scale = np.abs(trail[0]).max()
   assert np.abs(x - trail[0]).max() / scale < (1e-5 if dtype == "float32" else 0.03), "residual stream after the layer differs"
   assert row_err(got, ref) < TOL[dtype]
+  cut = run_cut(n, 1, toks, [7, 5, 1])               # short portions and single rows: the few-rows kernels of the same mechanism
+  assert row_err(cut, ref) < TOL[dtype]
   n.close()
 
 
