@@ -41,6 +41,16 @@ extern "C" {
 
 #define XOTB200_LM_MIX_LATENT_ATTN 0
 #define XOTB200_LM_MIX_DELTA_RULE 1
+#define XOTB200_LM_MIX_ATTENTION 2   /* grouped-query attention over a paged key/value cache (see xotb200_lm_layer)            */
+#define XOTB200_LM_MIX_GATED_DELTA 3 /* delta rule with one decay per head behind short causal convolutions                    */
+
+#define XOTB200_LM_FF_RELU2 0  /* W_down relu(W_up h)^2                                                                         */
+#define XOTB200_LM_FF_XIELU 1  /* W_down act(W_up h), act(z) = softplus(p) z^2 + z/2 (z > 0), (1/2 + softplus(q))(e^z - 1 - z) + z/2 (z <= 0);
+                                  p, q = the two entries of l<i>.mlp.act                                                         */
+#define XOTB200_LM_FF_MOE 2    /* mixture of gated experts W_down (silu(W_gate h) * W_up h), softmax router, group-limited top-k */
+
+#define XOTB200_LM_BLOCK_GROUP_RMS 0  /* x += norm1b(mixer(norm1(x))): grouped RMS norms before and after every sublayer          */
+#define XOTB200_LM_BLOCK_POST_LN 1    /* x += LN(mixer(x)): the sublayer reads the stream itself, layer norm (weight + bias) on its output */
 
 #define XOTB200_LM_ROT_INTERLEAVED 0 /* pairs (2i, 2i+1)        */
 #define XOTB200_LM_ROT_HALF 1        /* pairs (i, i + dims / 2) */
@@ -56,11 +66,34 @@ typedef struct xotb200_lm_layer {
   int32_t rot_dims;   /* how many leading entries of the rotated part are turned (<= rot_dim, even)           */
   int32_t rot_layout; /* XOTB200_LM_ROT_*                                                                     */
   int32_t window;     /* > 0: a query at position i sees i - window < j <= i; 0: every j <= i                 */
-  int32_t out_gate;   /* latent attention: 1 = one sigmoid gate per head on the mixer output                  */
+  int32_t out_gate;   /* attention: 1 = one sigmoid gate per head on the mixer output, 2 = one per output entry (heads * vdim) */
   int32_t low_rank;   /* delta rule: inner size of the decay branch                                           */
   int32_t ff;         /* feed-forward inner size (relu^2 between up and down); 0 = the layer has none         */
   float rot_base;
   float scale;        /* score scale                                                                          */
+  /* -- grouped-query attention (MIX_ATTENTION) and gated delta rule (MIX_GATED_DELTA) -------------------------------------
+   * MIX_ATTENTION: `heads` query heads of size `dim` share `kv_heads` key/value heads (query head a reads a / (heads / kv_heads)),
+   * values of size `vdim`; the cache holds per token [keys after their norm | values].  score = q.k * scale, then
+   * softcap * tanh(score / softcap) when softcap > 0, then - r1[a] * ln(1 + r2[a] * (i - j)) when dist_bias; visible keys: j <= i,
+   * i - j < window when window > 0, floor(i / chunk) == floor(j / chunk) when chunk > 0; softmax.
+   * MIX_GATED_DELTA: `kv_heads` query/key heads of size `dim`, `heads` value heads of size `vdim`; q, k, v pass a causal
+   * per-channel filter of `conv_taps` taps and silu; q, k unit vectors (q also / sqrt(dim)); per head S <- g S,
+   * S += k (beta (v - S^T k))^T, o = S^T q with g = exp(-exp(A_log) softplus(W_a h + dt_bias)), beta = sigmoid(W_b h);
+   * o / rms(o) * norm * silu(W_g h).  State: fp32 S [dim, vdim] per head + the last conv_taps - 1 filter inputs. */
+  int32_t kv_heads;
+  int32_t kv_from;    /* attention: -1 = own keys/values; else the (global) index of the earlier layer whose cache it reads */
+  int32_t chunk;      /* attention: > 0 = block-local causal mask with blocks of this many positions          */
+  int32_t qk_norm;    /* attention: 1 = per-head RMS norm of queries and keys (weights q.norm / k.norm of size dim) */
+  int32_t proj_bias;  /* attention: 1 = q, k, v projections have biases (q.b, k.b, v.b)                       */
+  int32_t dist_bias;  /* attention: 1 = logarithmic distance penalty with per-head r1, r2                     */
+  int32_t conv_taps;  /* gated delta rule: taps of the short convolutions                                     */
+  int32_t ff_kind;    /* XOTB200_LM_FF_*  (`ff` = inner size of the dense forms)                              */
+  int32_t experts;    /* FF_MOE: number of experts, each of inner size expert_ff                              */
+  int32_t expert_ff;
+  int32_t top;        /* FF_MOE: experts per token; weights = their softmax scores over ALL experts, not renormalised */
+  int32_t groups;     /* FF_MOE: experts form `groups` equal groups of neighbours (<= 1: no groups) ...        */
+  int32_t groups_keep;/* ... and only experts of the groups_keep groups with the largest best score can be chosen */
+  float softcap;
 } xotb200_lm_layer;
 
 typedef struct xotb200_lm_cfg {
@@ -72,6 +105,8 @@ typedef struct xotb200_lm_cfg {
   int32_t norm_groups;
   int32_t dtype;       /* XOTB200_LM_DTYPE_*                                   */
   float norm_eps;
+  int32_t block;         /* XOTB200_LM_BLOCK_*: how a layer wraps its sublayers; the final norm is of the same kind        */
+  int32_t max_positions; /* > 0: a learned position vector pos[p] is added to the embedding; requests hold at most this many tokens */
 } xotb200_lm_cfg;
 
 typedef struct xotb200_lm xotb200_lm;
@@ -85,6 +120,9 @@ int xotb200_lm_destroy(xotb200_lm* e);
 
 /* Weights.  Tensor names: embed, head, final.norm, l<i>.norm1 / norm1b / norm2 / norm2b, l<i>.mix.<t>, l<i>.mlp.up / down with
  * <t> in {dq, dq.norm, uq | q, dkv, dkv.norm, uk, uv, g, o} or {r, k, v, g, a, a.b, w1, w2, w0, norm, o}; linear weights [out, in].
+ * BLOCK_POST_LN models: pos, final.norm.b, l<i>.norm1 / norm1.b / norm2 / norm2.b; MIX_ATTENTION <t> in {q, q.b, q.norm, k, k.b,
+ * k.norm, v, v.b, r1, r2, g, o}; MIX_GATED_DELTA <t> in {q, q.conv, k, k.conv, v, v.conv, b, a, A_log, dt_bias, norm, g, o};
+ * l<i>.mlp.act (FF_XIELU); l<i>.mlp.router, l<i>.mlp.e<n>.gate / up / down (FF_MOE).
  * xotb200_lm_load_dir reads every *.safetensors of the directory (BF16 tensors) and is STRICT: a tensor of this shard that is
  * missing, has another shape or dtype, or an unknown tensor of an owned layer, is an error. */
 int xotb200_lm_load_dir(xotb200_lm* e, const char* dir);

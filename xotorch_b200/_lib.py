@@ -100,7 +100,9 @@ def load(path: os.PathLike | None = None) -> C.CDLL:
 # ---- libxotb200_lm.so: the layered-model engine (include/xotb200_lm.h) --------------------------------------------------
 LM_LIB_PATH = Path(__file__).resolve().parent / "lib" / "libxotb200_lm.so"
 LM_DTYPE_BF16, LM_DTYPE_F32 = 0, 2
-LM_MIX_LATENT_ATTN, LM_MIX_DELTA_RULE = 0, 1
+LM_MIX_LATENT_ATTN, LM_MIX_DELTA_RULE, LM_MIX_ATTENTION, LM_MIX_GATED_DELTA = 0, 1, 2, 3
+LM_FF_RELU2, LM_FF_XIELU, LM_FF_MOE = 0, 1, 2
+LM_BLOCK_GROUP_RMS, LM_BLOCK_POST_LN = 0, 1
 LM_ROT_INTERLEAVED, LM_ROT_HALF = 0, 1
 
 
@@ -110,13 +112,16 @@ class LmLayer(C.Structure):
     ("mixer", C.c_int32), ("heads", C.c_int32), ("dim", C.c_int32), ("vdim", C.c_int32), ("rot_dim", C.c_int32),
     ("kv_rank", C.c_int32), ("q_rank", C.c_int32), ("rot_dims", C.c_int32), ("rot_layout", C.c_int32), ("window", C.c_int32),
     ("out_gate", C.c_int32), ("low_rank", C.c_int32), ("ff", C.c_int32), ("rot_base", C.c_float), ("scale", C.c_float),
+    ("kv_heads", C.c_int32), ("kv_from", C.c_int32), ("chunk", C.c_int32), ("qk_norm", C.c_int32), ("proj_bias", C.c_int32),
+    ("dist_bias", C.c_int32), ("conv_taps", C.c_int32), ("ff_kind", C.c_int32), ("experts", C.c_int32), ("expert_ff", C.c_int32),
+    ("top", C.c_int32), ("groups", C.c_int32), ("groups_keep", C.c_int32), ("softcap", C.c_float),
   ]
 
 
 class LmCfg(C.Structure):
   _fields_ = [
     ("n_layers", C.c_int32), ("start_layer", C.c_int32), ("end_layer", C.c_int32), ("width", C.c_int32), ("vocab", C.c_int32),
-    ("norm_groups", C.c_int32), ("dtype", C.c_int32), ("norm_eps", C.c_float),
+    ("norm_groups", C.c_int32), ("dtype", C.c_int32), ("norm_eps", C.c_float), ("block", C.c_int32), ("max_positions", C.c_int32),
   ]
 
 
@@ -162,7 +167,7 @@ def load_lm(path: os.PathLike | None = None, build: bool = True) -> C.CDLL:
   p = Path(path) if path else Path(os.environ.get("XOTB200_LM_LIB", LM_LIB_PATH))
   if build and path is None and "XOTB200_LM_LIB" not in os.environ:
     src = Path(__file__).resolve().parent / "csrc"
-    deps = [src / n for n in ("layered.cu", "layered_kernels.cuh", "layered_tc.cuh", "prefill_tc.cuh", "kernels.cuh", "st_header.h")]
+    deps = [src / n for n in ("layered.cu", "layered_kernels.cuh", "layered_blocks.cuh", "layered_gqa.cuh", "layered_tc.cuh", "prefill_tc.cuh", "kernels.cuh", "st_header.h")]
     deps.append(src.parent.parent / "include" / "xotb200_lm.h")
     stale = p.exists() and any(d.exists() and d.stat().st_mtime > p.stat().st_mtime for d in deps)
     if not p.exists() or stale:

@@ -27,6 +27,8 @@
 
 #include "../../include/xotb200_lm.h"
 #include "layered_kernels.cuh"
+#include "layered_blocks.cuh"
+#include "layered_gqa.cuh"
 #include "layered_tc.cuh"
 #include "st_header.h"
 
@@ -83,9 +85,19 @@ struct LmLayer {
   int c_r, c_k, c_v, c_a, c_w1;                        // delta rule: columns (gate shares c_g)
   size_t w2, w0, a_b, onorm;
   size_t up, down;
+  // grouped-query attention: columns of q / k / v (gate: c_g), bias vector over the projection's columns, norm weights, penalties
+  int c_kk = 0, c_vv = 0;
+  size_t b_in = 0, q_norm = 0, k_norm = 0, r1 = 0, r2 = 0;
+  int kv_src = -1;                                     // local index of the layer whose pool this layer reads (itself when it has keys/values)
+  // gated delta rule: filter weights [channels, taps] (q, k, v channels in the projection's order), decay constants, column of beta
+  size_t conv_w = 0, a_log = 0, dt_bias = 0;
+  int c_b = 0, conv_ch = 0;
+  size_t conv_off = 0;                                 // float offset of the filter inputs inside a slot's state block
+  // feed-forward forms: xIELU parameters; mixture of experts: router [E, D], experts' [E][2 F, D] (gate rows, up rows) and [E][D, F]
+  size_t act_p = 0, router = 0, w_gu = 0, w_edown = 0;
   float* freqs = nullptr;                              // [rot_dims / 2] fp32 on the device
-  void* pool = nullptr;                                // latent pool [n_pages * P, kv_rank + rot_dim] of T
-  size_t state_off = 0;                                // delta rule: float offset of this layer's state inside a slot's block
+  void* pool = nullptr;                                // paged pool [n_pages * P, row] of T: latent + rotated key part, or keys + values
+  size_t state_off = 0;                                // delta rules: float offset of this layer's state inside a slot's block
 };
 
 struct GraphSlot {
@@ -120,6 +132,11 @@ struct xotb200_lm {
   // scratch (rows capacity m_cap)
   int m_cap = 0, want_cap = 0;
   float *x = nullptr, *y = nullptr, *proj = nullptr, *qraw = nullptr, *qfull = nullptr, *wlog = nullptr, *oraw = nullptr, *du = nullptr, *dau = nullptr, *logits = nullptr;
+  float *dkk = nullptr, *drr = nullptr, *cvb = nullptr, *moe_wts = nullptr;   // gated delta rule: write keys, read-out vectors, filtered channels; expert weights
+  int* moe_ids = nullptr;
+  void* mact = nullptr;                                // experts' inner activations [rows, top, F] of T
+  int max_conv = 0, max_top = 0, max_eff = 0, max_experts = 0;
+  size_t final_norm_b = 0, pos_table = 0;
   void *h = nullptr, *cqn = nullptr, *qn = nullptr, *olat = nullptr, *oh = nullptr, *act = nullptr, *th = nullptr, *hw = nullptr;
   void *q16 = nullptr, *cbuf = nullptr, *knx = nullptr, *vxx = nullptr;   // expanded prompt attention (bf16)
   size_t flash_keys_cap = 0;
@@ -157,7 +174,13 @@ static int build_layout(xotb200_lm* e, const xotb200_lm_layer* all) {
   const size_t al = 256 / e->esz;
   auto take = [&](size_t n) { size_t o = cur; cur = align_up(cur + n, al); return o; };
   auto dest = [&](const std::string& name, size_t off, int rows, int cols, int row_off) { e->dests[name] = Dest{off, rows, cols, row_off, false}; };
-  if (e->first) { e->embed = take((size_t)V * D); dest("embed", e->embed, V, D, 0); }
+  const bool post_ln = e->cfg.block == XOTB200_LM_BLOCK_POST_LN;
+  // the weight after a sublayer: a second grouped RMS norm ("norm1b"), or the bias of the closing layer norm ("norm1.b")
+  const std::string nb = post_ln ? ".b" : "b";
+  if (e->first) {
+    e->embed = take((size_t)V * D); dest("embed", e->embed, V, D, 0);
+    if (e->cfg.max_positions > 0) { e->pos_table = take((size_t)e->cfg.max_positions * D); dest("pos", e->pos_table, e->cfg.max_positions, D, 0); }
+  }
   for (int li = e->cfg.start_layer; li <= e->cfg.end_layer; ++li) {
     LmLayer L{};
     L.s = all[li];
@@ -165,7 +188,7 @@ static int build_layout(xotb200_lm* e, const xotb200_lm_layer* all) {
     const std::string p = "l" + std::to_string(li) + ".";
     REQUIRE(s.heads >= 1 && s.dim >= 1, "layer %d: heads and dim must be positive", li);
     L.norm1 = take(D); dest(p + "norm1", L.norm1, 1, D, 0);
-    L.norm1b = take(D); dest(p + "norm1b", L.norm1b, 1, D, 0);
+    L.norm1b = take(D); dest(p + "norm1" + nb, L.norm1b, 1, D, 0);
     if (s.mixer == XOTB200_LM_MIX_LATENT_ATTN) {
       const int H = s.heads, dn = s.dim, dr = s.rot_dim, dv = s.vdim, R = s.kv_rank, HQ = H * (dn + dr);
       REQUIRE(R >= 1 && R <= 512, "layer %d: kv_rank %d outside 1..512", li, R);
@@ -225,21 +248,118 @@ static int build_layout(xotb200_lm* e, const xotb200_lm_layer* all) {
       e->max_hd = std::max(e->max_hd, HD);
       e->max_lr = std::max(e->max_lr, s.low_rank);
       e->max_oh = std::max(e->max_oh, HD);
+    } else if (s.mixer == XOTB200_LM_MIX_ATTENTION) {
+      const int H = s.heads, G = s.kv_heads, dk = s.dim, dv = s.vdim;
+      const bool own = s.kv_from < 0;
+      REQUIRE(G >= 1 && H % G == 0, "layer %d: %d query heads do not divide into %d key/value heads", li, H, G);
+      REQUIRE(dv >= 1 && dv <= 256 && dk <= 1024, "layer %d: attention sizes dim %d (<= 1024) / vdim %d (1..256)", li, dk, dv);
+      REQUIRE(s.window >= 0 && s.chunk >= 0 && s.softcap >= 0.f, "layer %d: negative window, chunk or softcap", li);
+      REQUIRE(s.out_gate >= 0 && s.out_gate <= 2, "layer %d: unknown output gate %d", li, s.out_gate);
+      if (!own) {
+        REQUIRE(s.kv_from >= e->cfg.start_layer && s.kv_from < li, "layer %d reads the keys/values of layer %d, which is not an earlier layer of this shard", li,
+                s.kv_from);
+        const xotb200_lm_layer& o = all[s.kv_from];
+        REQUIRE(o.mixer == XOTB200_LM_MIX_ATTENTION && o.kv_from < 0 && o.kv_heads == G && o.dim == dk && o.vdim == dv,
+                "layer %d: layer %d does not hold keys/values of its shape", li, s.kv_from);
+        L.kv_src = s.kv_from - e->cfg.start_layer;
+      } else {
+        L.kv_src = li - e->cfg.start_layer;
+      }
+      // projection columns: q | k | v | gate   (k, v only with keys/values of its own)
+      L.c_q = 0; L.c_kk = H * dk; L.c_vv = L.c_kk + (own ? G * dk : 0); L.c_g = L.c_vv + (own ? G * dv : 0);
+      const int ng = s.out_gate == 2 ? H * dv : s.out_gate == 1 ? H : 0;
+      L.n_in = L.c_g + ng;
+      L.w_in = take((size_t)L.n_in * D);
+      dest(p + "mix.q", L.w_in, H * dk, D, L.c_q);
+      if (own) { dest(p + "mix.k", L.w_in, G * dk, D, L.c_kk); dest(p + "mix.v", L.w_in, G * dv, D, L.c_vv); }
+      if (ng) dest(p + "mix.g", L.w_in, ng, D, L.c_g);
+      if (s.proj_bias) {
+        L.b_in = take(L.n_in);                                 // zero where a projection has no bias (the blob starts zeroed)
+        dest(p + "mix.q.b", L.b_in + L.c_q, 1, H * dk, 0);
+        if (own) { dest(p + "mix.k.b", L.b_in + L.c_kk, 1, G * dk, 0); dest(p + "mix.v.b", L.b_in + L.c_vv, 1, G * dv, 0); }
+      }
+      if (s.qk_norm) {
+        L.q_norm = take(dk); dest(p + "mix.q.norm", L.q_norm, 1, dk, 0);
+        if (own) { L.k_norm = take(dk); dest(p + "mix.k.norm", L.k_norm, 1, dk, 0); }
+      }
+      if (s.dist_bias) {
+        L.r1 = take(H); dest(p + "mix.r1", L.r1, 1, H, 0);
+        L.r2 = take(H); dest(p + "mix.r2", L.r2, 1, H, 0);
+      }
+      L.wo = take((size_t)D * H * dv); dest(p + "mix.o", L.wo, D, H * dv, 0);
+      e->max_q = std::max(e->max_q, H * dk);
+      e->max_qfull = std::max(e->max_qfull, H * dk);
+      e->max_oh = std::max(e->max_oh, H * dv);
+    } else if (s.mixer == XOTB200_LM_MIX_GATED_DELTA) {
+      const int H = s.heads, G = s.kv_heads, dk = s.dim, dv = s.vdim, C = 2 * G * dk + H * dv;
+      REQUIRE(G >= 1 && H % G == 0, "layer %d: %d value heads do not divide into %d query/key heads", li, H, G);
+      REQUIRE(dk <= 256 && dv >= 1 && dv <= 256, "layer %d: delta-rule head sizes %d / %d above 256", li, dk, dv);
+      REQUIRE(s.conv_taps >= 1 && s.conv_taps <= 64, "layer %d: %d convolution taps (1..64)", li, s.conv_taps);
+      // projection columns: q | k | v (the filtered channels, in this order) | output gate | beta | decay logit
+      L.c_r = 0; L.c_k = G * dk; L.c_v = 2 * G * dk; L.c_g = C; L.c_b = C + H * dv; L.c_a = L.c_b + H;
+      L.conv_ch = C;
+      L.n_in = L.c_a + H;
+      L.w_in = take((size_t)L.n_in * D);
+      dest(p + "mix.q", L.w_in, G * dk, D, L.c_r);
+      dest(p + "mix.k", L.w_in, G * dk, D, L.c_k);
+      dest(p + "mix.v", L.w_in, H * dv, D, L.c_v);
+      dest(p + "mix.g", L.w_in, H * dv, D, L.c_g);
+      dest(p + "mix.b", L.w_in, H, D, L.c_b);
+      dest(p + "mix.a", L.w_in, H, D, L.c_a);
+      L.conv_w = take((size_t)C * s.conv_taps);
+      dest(p + "mix.q.conv", L.conv_w, G * dk, s.conv_taps, L.c_r);
+      dest(p + "mix.k.conv", L.conv_w, G * dk, s.conv_taps, L.c_k);
+      dest(p + "mix.v.conv", L.conv_w, H * dv, s.conv_taps, L.c_v);
+      L.a_log = take(H); dest(p + "mix.A_log", L.a_log, 1, H, 0);
+      L.dt_bias = take(H); dest(p + "mix.dt_bias", L.dt_bias, 1, H, 0);
+      L.onorm = take(dv); dest(p + "mix.norm", L.onorm, 1, dv, 0);
+      L.wo = take((size_t)D * H * dv); dest(p + "mix.o", L.wo, D, H * dv, 0);
+      L.state_off = e->state_floats;
+      e->state_floats += (size_t)H * dk * dv;
+      L.conv_off = e->state_floats;
+      e->state_floats += (size_t)(s.conv_taps - 1) * C;
+      e->max_hd = std::max(e->max_hd, H * std::max(dk, dv));
+      e->max_oh = std::max(e->max_oh, H * dv);
+      e->max_conv = std::max(e->max_conv, C);
     } else {
       REQUIRE(false, "layer %d: unknown mixer kind %d", li, s.mixer);
     }
     e->max_in = std::max(e->max_in, L.n_in);
-    if (s.ff > 0) {
+    const bool has_ff = s.ff_kind == XOTB200_LM_FF_MOE ? s.experts > 0 : s.ff > 0;
+    if (has_ff) {
       L.norm2 = take(D); dest(p + "norm2", L.norm2, 1, D, 0);
-      L.norm2b = take(D); dest(p + "norm2b", L.norm2b, 1, D, 0);
+      L.norm2b = take(D); dest(p + "norm2" + nb, L.norm2b, 1, D, 0);
+    }
+    if (s.ff_kind == XOTB200_LM_FF_MOE && has_ff) {
+      const int E = s.experts, F = s.expert_ff;
+      REQUIRE(F >= 1 && s.top >= 1 && s.top <= E && E <= 4096, "layer %d: %d experts of size %d, %d per token", li, E, F, s.top);
+      if (s.groups > 1)
+        REQUIRE(E % s.groups == 0 && s.groups_keep >= 1 && s.groups_keep <= s.groups && s.groups_keep * (E / s.groups) >= s.top,
+                "layer %d: %d experts in %d groups of which %d are kept cannot give %d experts per token", li, E, s.groups, s.groups_keep, s.top);
+      L.router = take((size_t)E * D); dest(p + "mlp.router", L.router, E, D, 0);
+      L.w_gu = take((size_t)E * 2 * F * D);
+      L.w_edown = take((size_t)E * D * F);
+      for (int x = 0; x < E; ++x) {
+        const std::string ep = p + "mlp.e" + std::to_string(x) + ".";
+        dest(ep + "gate", L.w_gu, F, D, x * 2 * F);
+        dest(ep + "up", L.w_gu, F, D, x * 2 * F + F);
+        dest(ep + "down", L.w_edown, D, F, x * D);
+      }
+      e->max_top = std::max(e->max_top, s.top);
+      e->max_eff = std::max(e->max_eff, F);
+      e->max_experts = std::max(e->max_experts, E);
+    } else if (has_ff) {
+      REQUIRE(s.ff_kind == XOTB200_LM_FF_RELU2 || s.ff_kind == XOTB200_LM_FF_XIELU, "layer %d: unknown feed-forward kind %d", li, s.ff_kind);
       L.up = take((size_t)s.ff * D); dest(p + "mlp.up", L.up, s.ff, D, 0);
       L.down = take((size_t)D * s.ff); dest(p + "mlp.down", L.down, D, s.ff, 0);
+      if (s.ff_kind == XOTB200_LM_FF_XIELU) { L.act_p = take(2); dest(p + "mlp.act", L.act_p, 1, 2, 0); }
       e->max_ff = std::max(e->max_ff, s.ff);
     }
     e->layers.push_back(L);
   }
   if (e->last) {
     e->final_norm = take(D); dest("final.norm", e->final_norm, 1, D, 0);
+    if (post_ln) { e->final_norm_b = take(D); dest("final.norm.b", e->final_norm_b, 1, D, 0); }
     e->head = take((size_t)V * D); dest("head", e->head, V, D, 0);
   }
   e->blob_elems = cur;
@@ -342,11 +462,11 @@ static int launch_ltc(xotb200_lm* e, const CUtensorMap& ma, const CUtensorMap& m
 // 1 = launched, 0 = not eligible (the caller falls back), < 0 = error
 template <typename TC, int EPI>
 static int product_tc(xotb200_lm* e, const bf16* A, long lda, long a_batch, const bf16* B, long ldb, long b_batch, TC* C, long ldc, long c_batch, int M,
-                      int N, int K, int batch) {
+                      int N, int K, int batch, const void* epi) {
   const int nt = (N > 64 && M > LTC_M) ? 128 : 64;   // one row tile: narrower column tiles, twice the CTAs streaming weights
   CUtensorMap ma, mb;
   if (!make_map3(&ma, A, M, K, lda, a_batch, batch, LTC_M) || !make_map3(&mb, B, N, K, ldb, b_batch, batch, nt)) return 0;
-  LtcArgs a{M, N, K, C, ldc, c_batch, e->d_err};
+  LtcArgs a{M, N, K, C, ldc, c_batch, e->d_err, static_cast<const bf16*>(epi)};
   if (nt == 128) TRY((launch_ltc<128, EPI, TC>(e, ma, mb, a, batch)));
   else TRY((launch_ltc<64, EPI, TC>(e, ma, mb, a, batch)));
   return 1;
@@ -354,13 +474,13 @@ static int product_tc(xotb200_lm* e, const bf16* A, long lda, long a_batch, cons
 
 template <typename TA, typename TB, typename TC, int EPI>
 static int product(xotb200_lm* e, const TA* A, long lda, long a_batch, const TB* B, long sbn, long sbk, long b_batch, TC* C, long ldc, long c_batch,
-                   int M, int N, int K, int batch) {
+                   int M, int N, int K, int batch, const void* epi = nullptr) {
   if (M == 0 || N == 0) return 0;
   const size_t smem = (size_t)M * K * 4;
   if constexpr (std::is_same<TA, bf16>::value && std::is_same<TB, bf16>::value && (EPI == 0 || !std::is_same<TC, float>::value)) {
     // 16-bit operands with more rows than the decode kernel takes: the tensor cores, when the operands can be described to TMA
     if (sbk == 1 && ((e->gemm_mode == 0 && M > GEMV_MAX_ROWS) || e->gemm_mode == 2)) {
-      const int r = product_tc<TC, EPI>(e, A, lda, a_batch, B, sbn, b_batch, C, ldc, c_batch, M, N, K, batch);
+      const int r = product_tc<TC, EPI>(e, A, lda, a_batch, B, sbn, b_batch, C, ldc, c_batch, M, N, K, batch, epi);
       if (r != 0) return r < 0 ? r : 0;
     }
   }
@@ -374,7 +494,8 @@ static int product(xotb200_lm* e, const TA* A, long lda, long a_batch, const TB*
   do {                                                                                                                         \
     auto kern = gemv_rows_kernel<TA, TB, TC, EPI, MR>;                                                                         \
     TRY(opt_in_smem(kern, sm));                                                                                                \
-    kern<<<dim3(blocks, 1, batch), 256, sm, e->stream>>>(A, lda, a_batch, B, sbn, b_batch, C, ldc, c_batch, M, N, K, wsplit); \
+    kern<<<dim3(blocks, 1, batch), 256, sm, e->stream>>>(A, lda, a_batch, B, sbn, b_batch, C, ldc, c_batch, M, N, K, wsplit,    \
+                                                         static_cast<const TB*>(epi));                                        \
   } while (0)
     if (M == 1) LAUNCH_GEMV(1);
     else if (M == 2) LAUNCH_GEMV(2);
@@ -383,7 +504,7 @@ static int product(xotb200_lm* e, const TA* A, long lda, long a_batch, const TB*
 #undef LAUNCH_GEMV
   } else {
     gemm_tiled_kernel<TA, TB, TC, EPI><<<dim3(cdiv(N, 64), cdiv(M, 64), batch), 256, 0, e->stream>>>(A, lda, a_batch, B, sbn, sbk, b_batch, C, ldc,
-                                                                                                  c_batch, M, N, K);
+                                                                                                  c_batch, M, N, K, static_cast<const TB*>(epi));
   }
   CK(cudaGetLastError());
   e->launches++;
@@ -421,6 +542,16 @@ static int ensure_scratch(xotb200_lm* e, int M, int n_want) {
     TRY(regrow(e->oraw, m * e->max_hd * 4));
     TRY(regrow(e->du, m * e->max_hd * 4));
     TRY(regrow(e->dau, m * e->max_hd * 4));
+    if (e->max_conv) {
+      TRY(regrow(e->dkk, m * e->max_hd * 4));
+      TRY(regrow(e->drr, m * e->max_hd * 4));
+      TRY(regrow(e->cvb, m * e->max_conv * 4));
+    }
+    if (e->max_top) {
+      TRY(regrow(e->moe_ids, m * e->max_top * 4));
+      TRY(regrow(e->moe_wts, m * e->max_top * 4));
+      TRY(regrow(e->mact, m * e->max_top * e->max_eff * z));
+    }
     TRY(regrow(e->h, m * D * z));
     TRY(regrow(e->cqn, m * e->max_qr * z));
     TRY(regrow(e->qn, m * e->max_hdn * z));
@@ -472,6 +603,7 @@ struct StepPlan {
   };
   std::map<int, Flash> flash;
   int max_len = 0;                                     // longest request after this step (bounds every key range)
+  int max_rows = 0;                                    // most rows one request brings
   bool any_short = true;                               // some request goes through the absorbed kernel
 };
 
@@ -597,18 +729,28 @@ static int attention_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
 }
 
 template <int KPT, int P, int NC>
-static int launch_delta(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
+static int launch_delta(xotb200_lm* e, LmLayer& L, const StepPlan& sp, DeltaSrc ks, DeltaSrc rs, DeltaSrc vs) {
   const xotb200_lm_layer& s = L.s;
   constexpr int CPW = (32 / P) * NC;
   const int warps = std::max(1, std::min(4, cdiv(s.vdim, CPW)));
   const dim3 grid(sp.n_seq * s.heads, cdiv(s.vdim, warps * CPW));
   const int HD = s.heads * s.dim;
-  const int vec4 = (s.dim % 4 == 0 && HD % 4 == 0 && L.n_in % 4 == 0 && L.c_r % 4 == 0 && L.c_k % 4 == 0 && L.c_v % 4 == 0) ? 1 : 0;
-  delta_rule_kernel<KPT, P, NC><<<grid, warps * 32, 0, e->stream>>>(e->proj, L.n_in, L.c_r, L.c_k, L.c_v, e->wlog, e->du, e->dau, sp.seqs, s.heads, s.dim,
-                                                                    s.vdim, e->state + L.state_off, e->state_floats, e->oraw, vec4);
+  const int vec4 = (s.dim % 4 == 0 && s.vdim % 4 == 0 && HD % 4 == 0 && (ks.ld | ks.col | rs.ld | rs.col | vs.ld | vs.col) % 4 == 0) ? 1 : 0;
+  delta_rule_kernel<KPT, P, NC><<<grid, warps * 32, 0, e->stream>>>(ks, rs, vs, e->wlog, e->du, e->dau, sp.seqs, s.heads, s.dim, s.vdim,
+                                                                    e->state + L.state_off, e->state_floats, e->oraw, vec4);
   CK(cudaGetLastError());
   e->launches++;
   return 0;
+}
+// the recurrence is bound by the instructions one warp issues per token (measured: ~2.8 cycles each): key rows over 8 lanes,
+// few columns per thread, four warps per block.  The variant is chosen by the larger of the key and value sizes.
+static int run_delta(xotb200_lm* e, LmLayer& L, const StepPlan& sp, DeltaSrc ks, DeltaSrc rs, DeltaSrc vs) {
+  const int d = std::max(L.s.dim, L.s.vdim);
+  if (d <= 16) return launch_delta<4, 4, 2>(e, L, sp, ks, rs, vs);
+  if (d <= 32) return launch_delta<8, 4, 2>(e, L, sp, ks, rs, vs);
+  if (d <= 64) return launch_delta<8, 8, 4>(e, L, sp, ks, rs, vs);
+  if (d <= 128) return launch_delta<16, 8, 2>(e, L, sp, ks, rs, vs);
+  return launch_delta<32, 8, 1>(e, L, sp, ks, rs, vs);
 }
 
 template <typename T>
@@ -625,18 +767,205 @@ static int delta_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
                                                                               s.heads, s.dim, M);
   CK(cudaGetLastError());
   e->launches++;
-  // the recurrence is bound by the instructions one warp issues per token (measured: ~2.8 cycles each): key rows over 8 lanes,
-  // few columns per thread, four warps per block
-  if (s.dim <= 16) TRY((launch_delta<4, 4, 2>(e, L, sp)));
-  else if (s.dim <= 32) TRY((launch_delta<8, 4, 2>(e, L, sp)));
-  else if (s.dim <= 64) TRY((launch_delta<8, 8, 4>(e, L, sp)));
-  else if (s.dim <= 128) TRY((launch_delta<16, 8, 2>(e, L, sp)));
-  else TRY((launch_delta<32, 8, 1>(e, L, sp)));
-  head_norm_gate_kernel<T><<<cdiv((long)M * s.heads, 8), 256, 0, e->stream>>>(e->oraw, at<T>(e, L.onorm), e->proj, L.n_in, L.c_g, static_cast<T*>(e->oh), s.heads,
-                                                                               s.vdim, e->cfg.norm_eps, M);
+  TRY(run_delta(e, L, sp, DeltaSrc{e->proj, L.n_in, L.c_k}, DeltaSrc{e->proj, L.n_in, L.c_r}, DeltaSrc{e->proj, L.n_in, L.c_v}));
+  head_norm_gate_kernel<T><<<cdiv((long)M * s.heads, 8), 256, 0, e->stream>>>(e->oraw, at<T>(e, L.onorm), s.vdim, e->proj, L.n_in, L.c_g, 0, static_cast<T*>(e->oh),
+                                                                               s.heads, s.vdim, e->cfg.norm_eps, M);
   CK(cudaGetLastError());
   e->launches++;
   TRY((product<T, T, float, 0>(e, static_cast<T*>(e->oh), HD, 0, at<T>(e, L.wo), HD, 1, 0, e->y, D, 0, M, D, HD, 1)));
+  return 0;
+}
+
+// rows of one request that share a CTA of the warp-per-(row, head) attention kernel: about 32 (row, head) pairs
+static int gqa_rows_per_item(const xotb200_lm_layer& s) { return std::max(1, 32 / (s.heads / s.kv_heads)); }
+
+// Few CTAs (decoding): the keys of an item are cut into runs so that the GPU is filled; each run at least one 32-key tile.
+// Returns the number of runs and their length.
+static int gqa_key_runs(const xotb200_lm* e, const xotb200_lm_layer& s, int n_items, int max_len, int* run) {
+  const int rep = s.heads / s.kv_heads, qpi = gqa_rows_per_item(s), pairs = qpi * rep, nw = std::min(32, pairs), ytiles = cdiv(pairs, nw);
+  int span = std::max(1, max_len);
+  if (s.window > 0) span = std::min(span, s.window + qpi);
+  if (s.chunk > 0) span = std::min(span, s.chunk);
+  int splits = 1;
+  const long ctas = (long)n_items * s.kv_heads * ytiles;
+  if (ctas > 0 && ctas < e->sm_count) splits = std::max(1, std::min(std::min(32, cdiv(span, 32)), cdiv(2 * e->sm_count, ctas)));
+  *run = cdiv(cdiv(span, splits), 32) * 32;
+  return cdiv(span, *run);
+}
+
+template <typename T>
+static int gqa_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
+  const xotb200_lm_layer& s = L.s;
+  const int D = e->cfg.width, M = sp.M, H = s.heads, G = s.kv_heads, dk = s.dim, dv = s.vdim, rep = H / G;
+  const bool own = s.kv_from < 0;
+  T* h = static_cast<T*>(e->h);
+  TRY((product<T, T, float, 0>(e, h, D, 0, at<T>(e, L.w_in), D, 1, 0, e->proj, L.n_in, 0, M, L.n_in, D, 1)));
+  const Paging pg{e->d_table, e->pages_per_slot, e->page_size};
+  T* pool = static_cast<T*>(e->layers[L.kv_src].pool);
+  const int slots = H + (own ? 2 * G : 0);
+  gqa_prepare_kernel<T><<<cdiv((long)M * slots, 8), 256, 0, e->stream>>>(
+      e->proj, L.n_in, L.c_q, L.c_kk, L.c_vv, s.proj_bias ? at<T>(e, L.b_in) : nullptr, s.qk_norm ? at<T>(e, L.q_norm) : nullptr,
+      s.qk_norm && own ? at<T>(e, L.k_norm) : nullptr, e->cfg.norm_eps, H, G, dk, dv, own ? 1 : 0, sp.row_slot, sp.row_pos, pg, pool, e->qfull, nullptr, M);
+  CK(cudaGetLastError());
+  e->launches++;
+  const GqaScore sc{s.scale, s.softcap, s.window, s.chunk, s.dist_bias ? at<T>(e, L.r1) : nullptr, s.dist_bias ? at<T>(e, L.r2) : nullptr};
+  const float* gate = s.out_gate ? e->proj : nullptr;
+  const int qpi = gqa_rows_per_item(s);
+  const auto& it = sp.items.at(-qpi);   // the lists of this mixer have negative keys
+  if (it.second > 0) {
+    const int pairs = qpi * rep, nw = std::min(32, pairs), ytiles = cdiv(pairs, nw);
+    const size_t smem = ((size_t)32 * ((dk + dv) | 1) + (size_t)nw * dk) * 4;
+    int run = 0;
+    const int splits = gqa_key_runs(e, s, it.second, sp.max_len, &run);
+    REQUIRE(splits == 1 || (size_t)M * H * splits * (2 + dv) <= e->part_cap, "internal: the key-run buffer was not sized for this step");
+    const dim3 grid(it.second, G * ytiles, splits);
+#define LAUNCH_GQA(NACC)                                                                                                                     \
+  do {                                                                                                                                       \
+    auto kern = gqa_attention_kernel<T, NACC>;                                                                                               \
+    TRY(opt_in_smem(kern, smem));                                                                                                            \
+    kern<<<grid, nw * 32, smem, e->stream>>>(e->qfull, pool, pg, it.first, H, G, dk, dv, sc, gate, s.out_gate, L.n_in, L.c_g,                \
+                                             static_cast<T*>(e->oh), run, e->part);                                                          \
+  } while (0)
+    if (dv <= 32) LAUNCH_GQA(1);
+    else if (dv <= 64) LAUNCH_GQA(2);
+    else if (dv <= 128) LAUNCH_GQA(4);
+    else LAUNCH_GQA(8);
+#undef LAUNCH_GQA
+    CK(cudaGetLastError());
+    e->launches++;
+    if (splits > 1) {
+      gqa_combine_kernel<T><<<dim3(it.second, cdiv(qpi * H, 8)), 256, 0, e->stream>>>(e->part, it.first, H, dv, splits, gate, s.out_gate, L.n_in, L.c_g,
+                                                                                     static_cast<T*>(e->oh));
+      CK(cudaGetLastError());
+      e->launches++;
+    }
+  }
+  TRY((product<T, T, float, 0>(e, static_cast<T*>(e->oh), (long)H * dv, 0, at<T>(e, L.wo), (long)H * dv, 1, 0, e->y, D, 0, M, D, H * dv, 1)));
+  return 0;
+}
+
+template <typename T>
+static int gated_delta_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
+  const xotb200_lm_layer& s = L.s;
+  const int D = e->cfg.width, M = sp.M, H = s.heads, G = s.kv_heads, dk = s.dim, dv = s.vdim, C = L.conv_ch;
+  T* h = static_cast<T*>(e->h);
+  TRY((product<T, T, float, 0>(e, h, D, 0, at<T>(e, L.w_in), D, 1, 0, e->proj, L.n_in, 0, M, L.n_in, D, 1)));
+  float* cstate = e->state + L.conv_off;
+  const int zrows = std::max(1, std::min(128, cdiv(sp.max_rows, 8)));
+  short_conv_silu_kernel<T><<<dim3(sp.n_seq, cdiv(C, 256), zrows), 256, 0, e->stream>>>(e->proj, L.n_in, 0, C, at<T>(e, L.conv_w), s.conv_taps, sp.seqs, cstate,
+                                                                                        e->state_floats, e->cvb);
+  CK(cudaGetLastError());
+  e->launches++;
+  if (s.conv_taps > 1) {
+    conv_state_update_kernel<<<dim3(sp.n_seq, cdiv(C, 256)), 256, 0, e->stream>>>(e->proj, L.n_in, 0, C, s.conv_taps, sp.seqs, cstate, e->state_floats);
+    CK(cudaGetLastError());
+    e->launches++;
+  }
+  gated_delta_prepare_kernel<T><<<cdiv((long)M * H, 8), 256, 0, e->stream>>>(e->cvb, C, e->proj, L.n_in, L.c_b, L.c_a, at<T>(e, L.a_log), at<T>(e, L.dt_bias), e->wlog,
+                                                                            e->du, e->dau, e->dkk, e->drr, H, G, dk, M);
+  CK(cudaGetLastError());
+  e->launches++;
+  TRY(run_delta(e, L, sp, DeltaSrc{e->dkk, H * dk, 0}, DeltaSrc{e->drr, H * dk, 0}, DeltaSrc{e->cvb, C, L.c_v}));
+  head_norm_gate_kernel<T><<<cdiv((long)M * H, 8), 256, 0, e->stream>>>(e->oraw, at<T>(e, L.onorm), 0, e->proj, L.n_in, L.c_g, 1, static_cast<T*>(e->oh), H, dv,
+                                                                       e->cfg.norm_eps, M);
+  CK(cudaGetLastError());
+  e->launches++;
+  TRY((product<T, T, float, 0>(e, static_cast<T*>(e->oh), (long)H * dv, 0, at<T>(e, L.wo), (long)H * dv, 1, 0, e->y, D, 0, M, D, H * dv, 1)));
+  return 0;
+}
+
+static bool layer_has_ff(const xotb200_lm_layer& s) { return s.ff_kind == XOTB200_LM_FF_MOE ? s.experts > 0 : s.ff > 0; }
+
+// the feed-forward of a layer: h (T) -> y (fp32)
+template <typename T>
+static int feed_forward(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
+  const xotb200_lm_layer& s = L.s;
+  const int D = e->cfg.width, M = sp.M;
+  T* h = static_cast<T*>(e->h);
+  if (s.ff_kind == XOTB200_LM_FF_MOE) {
+    const int E = s.experts, F = s.expert_ff, top = s.top;
+    moe_router_kernel<T><<<cdiv(M, 4), 128, (size_t)4 * (E + 32) * 4, e->stream>>>(h, D, at<T>(e, L.router), E, s.groups, s.groups_keep, top, e->moe_ids, e->moe_wts, M);
+    CK(cudaGetLastError());
+    e->launches++;
+    {
+      auto kern = moe_rows_up_kernel<T>;
+      TRY(opt_in_smem(kern, (size_t)D * 4));
+      kern<<<dim3(M, top, std::max(1, std::min(cdiv(F, 8), 64))), 256, (size_t)D * 4, e->stream>>>(h, D, at<T>(e, L.w_gu), F, e->moe_ids, top, static_cast<T*>(e->mact));
+      CK(cudaGetLastError());
+      e->launches++;
+    }
+    {
+      auto kern = moe_rows_down_kernel<T>;
+      TRY(opt_in_smem(kern, (size_t)top * F * 4));
+      kern<<<dim3(M, std::max(1, std::min(cdiv(D, 8), 64))), 256, (size_t)top * F * 4, e->stream>>>(static_cast<T*>(e->mact), F, at<T>(e, L.w_edown), D, e->moe_ids, e->moe_wts,
+                                                                                                   top, e->y);
+      CK(cudaGetLastError());
+      e->launches++;
+    }
+    return 0;
+  }
+  if (s.ff_kind == XOTB200_LM_FF_XIELU)
+    TRY((product<T, T, T, 2>(e, h, D, 0, at<T>(e, L.up), D, 1, 0, static_cast<T*>(e->act), s.ff, 0, M, s.ff, D, 1, at<T>(e, L.act_p))));
+  else
+    TRY((product<T, T, T, 1>(e, h, D, 0, at<T>(e, L.up), D, 1, 0, static_cast<T*>(e->act), s.ff, 0, M, s.ff, D, 1)));
+  TRY((product<T, T, float, 0>(e, static_cast<T*>(e->act), s.ff, 0, at<T>(e, L.down), s.ff, 1, 0, e->y, D, 0, M, D, s.ff, 1)));
+  return 0;
+}
+
+template <typename T>
+static int run_mixer(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
+  switch (L.s.mixer) {
+    case XOTB200_LM_MIX_LATENT_ATTN: return attention_layer<T>(e, L, sp);
+    case XOTB200_LM_MIX_DELTA_RULE: return delta_layer<T>(e, L, sp);
+    case XOTB200_LM_MIX_ATTENTION: return gqa_layer<T>(e, L, sp);
+    default: return gated_delta_layer<T>(e, L, sp);
+  }
+}
+
+// layers of the form x += LN(sublayer(x)): the sublayer reads the stream itself (its T copy h), a layer norm closes it
+template <typename T>
+static int run_layers_post_ln(xotb200_lm* e, const StepPlan& sp, int n_want) {
+  const int D = e->cfg.width, M = sp.M;
+  const float eps = e->cfg.norm_eps;
+  T* h = static_cast<T*>(e->h);
+  const int nt = std::min(1024, std::max(128, cdiv(D, 4 * 32) * 32));
+  auto kern = residual_layernorm_kernel<T>;
+  TRY(opt_in_smem(kern, (size_t)D * 4));
+  auto close = [&](size_t w, size_t b) -> int {
+    kern<<<M, nt, (size_t)D * 4, e->stream>>>(e->x, e->y, at<T>(e, w), at<T>(e, b), h, nullptr, D, eps);
+    CK(cudaGetLastError());
+    e->launches++;
+    return 0;
+  };
+  if (e->first) {
+    embed_pos_rows_kernel<T><<<M, 128, 0, e->stream>>>(at<T>(e, e->embed), e->cfg.max_positions > 0 ? at<T>(e, e->pos_table) : nullptr, sp.tokens, sp.row_pos,
+                                                       e->x, h, D);
+  } else {
+    cast_rows_kernel<T><<<std::min(4096, cdiv((long)M * D, 256)), 256, 0, e->stream>>>(e->x, h, (size_t)M * D);
+  }
+  CK(cudaGetLastError());
+  e->launches++;
+  for (size_t li = 0; li < e->layers.size(); ++li) {
+    LmLayer& L = e->layers[li];
+    TRY(run_mixer<T>(e, L, sp));
+    TRY(close(L.norm1, L.norm1b));
+    if (layer_has_ff(L.s)) {
+      TRY(feed_forward<T>(e, L, sp));
+      TRY(close(L.norm2, L.norm2b));
+    }
+    if (e->trace) CK(cudaMemcpyAsync(e->trace_buf + li * (size_t)M * D, e->x, (size_t)M * D * 4, cudaMemcpyDeviceToDevice, e->stream));
+  }
+  if (e->trace) e->trace_floats = e->layers.size() * (size_t)M * D;
+  if (e->last && n_want > 0) {
+    T* hw = static_cast<T*>(e->hw);
+    kern<<<n_want, nt, (size_t)D * 4, e->stream>>>(e->x, nullptr, at<T>(e, e->final_norm), at<T>(e, e->final_norm_b), hw, sp.want, D, eps);
+    CK(cudaGetLastError());
+    e->launches++;
+    TRY((product<T, T, float, 0>(e, hw, D, 0, at<T>(e, e->head), D, 1, 0, e->logits, e->cfg.vocab, 0, n_want, e->cfg.vocab, D, 1)));
+    argmax_rows_kernel<<<n_want, 1024, 0, e->stream>>>(e->logits, e->cfg.vocab, e->d_argmax);
+    CK(cudaGetLastError());
+    e->launches++;
+  }
   return 0;
 }
 
@@ -649,6 +978,7 @@ static int norm_threads(int D, int G) {
 
 template <typename T>
 static int run_layers(xotb200_lm* e, const StepPlan& sp, int n_want) {
+  if (e->cfg.block == XOTB200_LM_BLOCK_POST_LN) return run_layers_post_ln<T>(e, sp, n_want);
   const int D = e->cfg.width, G = e->cfg.norm_groups, M = sp.M;
   const float eps = e->cfg.norm_eps;
   T* h = static_cast<T*>(e->h);
@@ -672,14 +1002,12 @@ static int run_layers(xotb200_lm* e, const StepPlan& sp, int n_want) {
   for (size_t li = 0; li < e->layers.size(); ++li) {
     LmLayer& L = e->layers[li];
     TRY(open(at<T>(e, L.norm1)));
-    if (L.s.mixer == XOTB200_LM_MIX_LATENT_ATTN) TRY(attention_layer<T>(e, L, sp));
-    else TRY(delta_layer<T>(e, L, sp));
+    TRY(run_mixer<T>(e, L, sp));
     pend_y = e->y;
     pend_w = at<T>(e, L.norm1b);
-    if (L.s.ff > 0) {
+    if (layer_has_ff(L.s)) {
       TRY(open(at<T>(e, L.norm2)));
-      TRY((product<T, T, T, 1>(e, h, D, 0, at<T>(e, L.up), D, 1, 0, static_cast<T*>(e->act), L.s.ff, 0, M, L.s.ff, D, 1)));
-      TRY((product<T, T, float, 0>(e, static_cast<T*>(e->act), L.s.ff, 0, at<T>(e, L.down), L.s.ff, 1, 0, e->y, D, 0, M, D, L.s.ff, 1)));
+      TRY(feed_forward<T>(e, L, sp));
       pend_y = e->y;
       pend_w = at<T>(e, L.norm2b);
     }
@@ -727,6 +1055,8 @@ int xotb200_lm_create(const xotb200_lm_cfg* cfg, const xotb200_lm_layer* layers,
           "bad layer range [%d, %d] of %d", cfg->start_layer, cfg->end_layer, cfg->n_layers);
   REQUIRE(cfg->width >= 1 && cfg->vocab >= 1, "width and vocab must be positive");
   REQUIRE(cfg->norm_groups >= 1 && cfg->width % cfg->norm_groups == 0, "width %d is not a multiple of norm_groups %d", cfg->width, cfg->norm_groups);
+  REQUIRE(cfg->block == XOTB200_LM_BLOCK_GROUP_RMS || cfg->block == XOTB200_LM_BLOCK_POST_LN, "unknown block form %d", cfg->block);
+  REQUIRE(cfg->max_positions >= 0, "negative max_positions");
   int ndev = 0;
   CK(cudaGetDeviceCount(&ndev));
   REQUIRE(device >= 0 && device < ndev, "device %d out of range (%d visible)", device, ndev);
@@ -780,7 +1110,7 @@ int xotb200_lm_destroy(xotb200_lm* e) {
   free_state(e);
   for (auto& L : e->layers)
     if (L.freqs) cudaFree(L.freqs);
-  void* ptrs[] = {e->du, e->dau, e->part, e->q16, e->cbuf, e->knx, e->vxx, e->blob, e->d_stage, e->x, e->y, e->proj, e->qraw, e->qfull, e->wlog, e->oraw, e->logits, e->h, e->cqn, e->qn, e->olat, e->oh, e->act,
+  void* ptrs[] = {e->dkk, e->drr, e->cvb, e->moe_ids, e->moe_wts, e->mact, e->du, e->dau, e->part, e->q16, e->cbuf, e->knx, e->vxx, e->blob, e->d_stage, e->x, e->y, e->proj, e->qraw, e->qfull, e->wlog, e->oraw, e->logits, e->h, e->cqn, e->qn, e->olat, e->oh, e->act,
                   e->th, e->hw, e->d_argmax, e->trace_buf};
   for (void* p : ptrs)
     if (p) cudaFree(p);
@@ -823,7 +1153,12 @@ int xotb200_lm_init_synthetic(xotb200_lm* e, uint64_t seed) {
     const std::string& name = kv.first;
     const size_t n = (size_t)d.rows * d.cols, off = d.elem_off + (size_t)d.row_off * d.cols;
     float mean = 0.f, dev = 1.0f / sqrtf((float)d.cols);
-    if (name.find("norm") != std::string::npos) { mean = 1.f; dev = 0.1f; }
+    const auto ends = [&](const char* suf) { const size_t n = strlen(suf); return name.size() >= n && name.compare(name.size() - n, n, suf) == 0; };
+    if (ends(".r1")) { mean = 0.1f; dev = 0.03f; }              // distance penalties stay positive
+    else if (ends(".r2")) { mean = 1.f; dev = 0.2f; }
+    else if (ends(".b") && d.rows == 1) dev = 0.1f;            // biases of projections and layer norms
+    else if (ends(".A_log")) dev = 0.3f;
+    else if (name.find("norm") != std::string::npos) { mean = 1.f; dev = 0.1f; }
     else if (d.rows == 1) dev = 0.5f;                  // biases of the delta-rule gates
     else if (name == "embed") dev = 1.f;
     const int grid = (int)std::min<size_t>(8192, (n + 255) / 256);
@@ -922,12 +1257,15 @@ int xotb200_lm_begin(xotb200_lm* e, int max_tokens, int max_requests, int page_s
   // every live request may hold one partly filled page: max_requests pages of slack
   e->n_pages = cdiv(max_tokens, P) + max_requests;
   e->pages_per_slot = cdiv(max_tokens, P) + 1;
-  for (auto& L : e->layers)
-    if (L.s.mixer == XOTB200_LM_MIX_LATENT_ATTN) {
-      const size_t bytes = (size_t)e->n_pages * P * (L.s.kv_rank + L.s.rot_dim) * e->esz;
-      CK(cudaMalloc(&L.pool, bytes));
-      CK(cudaMemsetAsync(L.pool, 0, bytes, e->stream));
-    }
+  for (auto& L : e->layers) {
+    size_t row = 0;                                    // elements a token holds in this layer's pool
+    if (L.s.mixer == XOTB200_LM_MIX_LATENT_ATTN) row = (size_t)L.s.kv_rank + L.s.rot_dim;
+    else if (L.s.mixer == XOTB200_LM_MIX_ATTENTION && L.s.kv_from < 0) row = (size_t)L.s.kv_heads * (L.s.dim + L.s.vdim);
+    if (!row) continue;
+    const size_t bytes = (size_t)e->n_pages * P * row * e->esz;
+    CK(cudaMalloc(&L.pool, bytes));
+    CK(cudaMemsetAsync(L.pool, 0, bytes, e->stream));
+  }
   const size_t tab = (size_t)max_requests * e->pages_per_slot;
   CK(cudaHostAlloc(&e->h_table, tab * 4, cudaHostAllocDefault));
   memset(e->h_table, 0, tab * 4);
@@ -986,6 +1324,8 @@ int xotb200_lm_step(xotb200_lm* e, int n_seq, const int32_t* slots, const int32_
     REQUIRE(counts[i] >= 1, "request %d brings %d rows", i, counts[i]);
     const int len = e->slot_len[slots[i]] + counts[i];
     REQUIRE(cdiv(len, P) <= e->pages_per_slot, "slot %d would hold %d tokens, more than the cache was sized for", slots[i], len);
+    REQUIRE(e->cfg.max_positions == 0 || len <= e->cfg.max_positions, "slot %d would hold %d tokens, the model has %d positions", slots[i], len,
+            e->cfg.max_positions);
     need_pages += cdiv(len, P) - e->slot_pages[slots[i]];
     M += counts[i];
   }
@@ -1004,6 +1344,9 @@ int xotb200_lm_step(xotb200_lm* e, int n_seq, const int32_t* slots, const int32_
       const int q = std::max(1, 32 / L.s.heads);
       if (std::find(qpis.begin(), qpis.end(), q) == qpis.end()) qpis.push_back(q);
       if (use_flash && std::find(windows.begin(), windows.end(), L.s.window) == windows.end()) windows.push_back(L.s.window);
+    } else if (L.s.mixer == XOTB200_LM_MIX_ATTENTION) {
+      const int q = -gqa_rows_per_item(L.s);             // negative: a list of the key/value-cache attention (its own rule for long portions)
+      if (std::find(qpis.begin(), qpis.end(), q) == qpis.end()) qpis.push_back(q);
     }
   std::vector<int>& st = e->stage_build;
   st.assign(3 * (size_t)M + n_want, 0);
@@ -1026,6 +1369,7 @@ int xotb200_lm_step(xotb200_lm* e, int n_seq, const int32_t* slots, const int32_
     e->slot_len[sl] = len1;
     seqs[i] = Item{row, counts[i], sl, len0};
     sp.max_len = std::max(sp.max_len, len1);
+    sp.max_rows = std::max(sp.max_rows, counts[i]);
     for (int t = 0; t < counts[i]; ++t, ++row) {
       st[row] = e->first ? tokens[row] : 0;
       st[M + row] = sl;
@@ -1038,13 +1382,15 @@ int xotb200_lm_step(xotb200_lm* e, int n_seq, const int32_t* slots, const int32_
   auto is_long = [&](int i) { return use_flash && counts[i] >= FLASH_MIN_ROWS; };
   std::map<int, std::pair<size_t, int>> item_off;
   sp.any_short = false;
-  for (int q : qpis) {
+  auto is_long_gqa = [&](int) { return false; };
+  for (int qk : qpis) {
     std::vector<Item> it;
+    const int q = qk < 0 ? -qk : qk;
     for (int i = 0; i < n_seq; ++i)
-      if (!is_long(i))
+      if (qk < 0 ? !is_long_gqa(i) : !is_long(i))
         for (int t = 0; t < counts[i]; t += q) it.push_back(Item{seqs[i].row0 + t, std::min(q, counts[i] - t), seqs[i].slot, seqs[i].pos0 + t});
-    item_off[q] = {push(it.data(), 4 * it.size()), (int)it.size()};
-    if (!it.empty()) sp.any_short = true;
+    item_off[qk] = {push(it.data(), 4 * it.size()), (int)it.size()};
+    if (!it.empty() && qk > 0) sp.any_short = true;
   }
   struct FlashOff { size_t reqs, tiles; int n_reqs, n_tiles, n_keys, max_keys; };
   std::map<int, FlashOff> flash_off;
@@ -1094,6 +1440,14 @@ int xotb200_lm_step(xotb200_lm* e, int n_seq, const int32_t* slots, const int32_
   // attention kernel cuts the keys into runs).
   const bool decode_shape = e->graphs_on && e->first && !e->trace && M == n_seq;
   sp.max_len = decode_shape ? cdiv(sp.max_len, 256) * 256 : sp.max_len;
+  // the key-run buffer is sized before anything is captured: a captured step must not replace a buffer
+  for (auto& L : e->layers)
+    if (L.s.mixer == XOTB200_LM_MIX_ATTENTION) {
+      int run = 0;
+      const int splits = gqa_key_runs(e, L.s, item_off[-gqa_rows_per_item(L.s)].second, sp.max_len, &run);
+      const size_t need = splits > 1 ? (size_t)M * L.s.heads * splits * (2 + L.s.vdim) : 0;
+      if (need > e->part_cap) { drop_graphs(e); TRY(regrow(e->part, need * 4)); e->part_cap = need; }
+    }
   GraphSlot* gs = nullptr;
   if (decode_shape) {
     const std::array<long, 5> key{n_seq, n_want, (logits_f32 ? 1 : 0) | (argmax_i32 ? 2 : 0), sp.max_len, (long)off};

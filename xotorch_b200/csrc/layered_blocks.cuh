@@ -1,0 +1,257 @@
+// layered_blocks.cuh — device code of the layered-model engine for models whose layers are  x += LN(sublayer(x))  (the sublayer
+// reads the residual stream itself, a layer norm with weight and bias closes it), with a learned position table, short causal
+// convolutions in front of a gated delta rule, the two-sided xIELU activation and mixtures of gated experts.
+//
+// Number formats as in layered_kernels.cuh: T is the storage type of weights and GEMM inputs (bf16 serving, float in the 32-bit
+// mode); the residual stream, norms, router, decays, step sizes, unit vectors and every state are fp32 whatever T is.
+#pragma once
+#include "layered_kernels.cuh"
+
+namespace xl {
+
+// sum over the block (all threads get it); `red` holds 32 floats; ends with a barrier so `red` can be reused at once
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = lane < nw ? red[lane] : 0.f;
+  t = warp_sum(t);
+  __syncthreads();
+  return t;
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// embedding with a learned position table:  x[m, :] = embed[token[m], :] + pos[row_pos[m], :]  (fp32), and its T copy h (the
+// operand of the first sublayer's products).  pos_table may be NULL.
+// ---------------------------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void embed_pos_rows_kernel(const T* __restrict__ embed, const T* __restrict__ pos_table, const int* __restrict__ tokens,
+                                      const int* __restrict__ row_pos, float* __restrict__ x, T* __restrict__ h, int D) {
+  const int m = blockIdx.x;
+  const T* src = embed + (size_t)tokens[m] * D;
+  const T* ps = pos_table ? pos_table + (size_t)row_pos[m] * D : nullptr;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    const float v = ldf(src + d) + (ps ? ldf(ps + d) : 0.f);
+    x[(size_t)m * D + d] = v;
+    if (h) stf(h + (size_t)m * D + d, v);
+  }
+}
+// the T copy of an fp32 stream (a later shard starts from the residual stream it is given)
+template <typename T>
+__global__ void cast_rows_kernel(const float* __restrict__ x, T* __restrict__ h, size_t n) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) stf(h + i, x[i]);
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// Layer norm that closes a sublayer:   x[m] += (y[m] - mean) / sqrt(var + eps) * w + b ;   h[m] = T(x[m])     (y != NULL)
+// or norms gathered rows of the stream: h[m] = T((x[src_rows[m]] - mean) / sqrt(var + eps) * w + b)            (y == NULL)
+// var = mean of the squared deviations (two passes over the row, which waits in shared memory).  One block per row;
+// dynamic shared memory: D floats.
+// ---------------------------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void residual_layernorm_kernel(float* __restrict__ x, const float* __restrict__ y, const T* __restrict__ w, const T* __restrict__ b,
+                                          T* __restrict__ h, const int* __restrict__ src_rows, int D, float eps) {
+  extern __shared__ float ln_row[];
+  __shared__ float red[32];
+  const int m = blockIdx.x;
+  const float* in = y ? y + (size_t)m * D : x + (size_t)(src_rows ? src_rows[m] : m) * D;
+  float s = 0.f;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) { const float v = in[d]; ln_row[d] = v; s += v; }
+  const float mean = block_sum(s, red) / (float)D;
+  float q = 0.f;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) { const float c = ln_row[d] - mean; q = fmaf(c, c, q); }
+  const float rstd = 1.0f / sqrtf(block_sum(q, red) / (float)D + eps);
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float v = (ln_row[d] - mean) * rstd * ldf(w + d) + ldf(b + d);
+    if (y) {
+      v += x[(size_t)m * D + d];
+      x[(size_t)m * D + d] = v;
+    }
+    if (h) stf(h + (size_t)m * D + d, v);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// Short causal convolution + silu on C channels of a projection output:
+//   out[m, c] = silu( sum_{i < taps} w[c, i] * in(pos_m - (taps - 1 - i), c) )
+// in(p, c) is the projection of the request's token at position p: a row of this step when p >= the step's first position of the
+// request, else one of the last taps-1 inputs of earlier steps, kept per slot in `state` ([taps - 1][C] fp32, zero at the start
+// of a request, so positions before 0 read as zero).  grid (requests, ceil(C / 256), row lanes).
+// conv_state_update_kernel then moves the window: it must run after every reader of the old state.
+// ---------------------------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void short_conv_silu_kernel(const float* __restrict__ proj, int ld, int col0, int C, const T* __restrict__ w, int taps,
+                                       const Item* __restrict__ seqs, const float* __restrict__ state, size_t state_slot_stride,
+                                       float* __restrict__ out) {
+  const Item sq = seqs[blockIdx.x];
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const float* st = state + (size_t)sq.slot * state_slot_stride;
+  for (int t = blockIdx.z; t < sq.n_rows; t += gridDim.z) {
+    float acc = 0.f;
+    for (int i = 0; i < taps; ++i) {
+      const int back = taps - 1 - i, src = t - back;           // row of this step, or (negative) before it
+      const float v = src >= 0 ? proj[(size_t)(sq.row0 + src) * ld + col0 + c] : st[(size_t)(src + taps - 1) * C + c];
+      acc = fmaf(ldf(w + (size_t)c * taps + i), v, acc);
+    }
+    out[(size_t)(sq.row0 + t) * C + c] = siluf_(acc);
+  }
+}
+__global__ void conv_state_update_kernel(const float* __restrict__ proj, int ld, int col0, int C, int taps, const Item* __restrict__ seqs,
+                                         float* __restrict__ state, size_t state_slot_stride) {
+  const Item sq = seqs[blockIdx.x];
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  float* st = state + (size_t)sq.slot * state_slot_stride;
+  for (int i = 0; i < taps - 1; ++i) {                         // increasing i: entry i + n_rows is still the old one when it is read
+    const int src = sq.n_rows + i - (taps - 1);
+    st[(size_t)i * C + c] = src >= 0 ? proj[(size_t)(sq.row0 + src) * ld + col0 + c] : st[(size_t)(i + sq.n_rows) * C + c];
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// Per-token vectors of the gated delta rule, in the form delta_rule_kernel takes (S <- diag(w) S - au (u^T S) + kk v^T, o = S^T r,
+// both products on the old S).  With unit key k, step size beta and decay g of the head:
+//   S <- g S;  S += k (beta (v - S^T k))^T      ==      w = g (all rows),  u = k,  au = beta g k,  kk = beta k.
+// cv [M, C] holds the filtered q (G * dk), k (G * dk), v (H * dv) channels; value head a reads query/key head a / (H / G).
+// proj columns col_b + a / col_a + a are the step-size and decay logits.  One warp per (row, value head).
+// ---------------------------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void gated_delta_prepare_kernel(const float* __restrict__ cv, int C, const float* __restrict__ proj, int ld, int col_b, int col_a,
+                                           const T* __restrict__ a_log, const T* __restrict__ dt_bias, float* __restrict__ w_out,
+                                           float* __restrict__ u_out, float* __restrict__ au_out, float* __restrict__ kk_out,
+                                           float* __restrict__ r_out, int H, int G, int dk, int M) {
+  const int idx = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (idx >= M * H) return;
+  const size_t m = idx / H;
+  const int a = idx % H, kh = a / (H / G);
+  const float* q = cv + m * C + (size_t)kh * dk;
+  const float* k = cv + m * C + (size_t)G * dk + (size_t)kh * dk;
+  float sq = 0.f, sk = 0.f;
+  for (int i = lane; i < dk; i += 32) { sq = fmaf(q[i], q[i], sq); sk = fmaf(k[i], k[i], sk); }
+  const float iq = 1.0f / (sqrtf(warp_sum(sq) + 1e-6f) * sqrtf((float)dk)), ik = 1.0f / sqrtf(warp_sum(sk) + 1e-6f);
+  const float beta = sigmoidf_(proj[m * ld + col_b + a]);
+  const float g = expf(-expf(ldf(a_log + a)) * softplusf_(proj[m * ld + col_a + a] + ldf(dt_bias + a)));
+  for (int i = lane; i < dk; i += 32) {
+    const size_t o = m * (size_t)(H * dk) + (size_t)a * dk + i;
+    const float ku = k[i] * ik;
+    w_out[o] = g;
+    u_out[o] = ku;
+    au_out[o] = beta * g * ku;
+    kk_out[o] = beta * ku;
+    r_out[o] = q[i] * iq;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// Mixture of experts, router: logits z = W_r h in fp32 (h in T), scores s = softmax(z) over all E experts; experts form `groups`
+// equal groups of neighbours, a group's score is its best expert's, only experts of the `keep` best groups can be chosen; the
+// `top` best of those are the token's experts, weighted by their s (not renormalised).  Ties go to the lower index.
+// One warp per row; dynamic shared memory: warps * E floats.
+// ---------------------------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void moe_router_kernel(const T* __restrict__ h, int D, const T* __restrict__ w_router, int E, int groups, int keep, int top,
+                                  int* __restrict__ ids, float* __restrict__ wts, int M) {
+  extern __shared__ float rsm[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (m >= M) return;
+  float* s = rsm + (size_t)warp * (E + 32);                    // [E] scores, then [32] group flags scratch
+  const T* hr = h + (size_t)m * D;
+  for (int e = 0; e < E; ++e) {
+    const T* wr = w_router + (size_t)e * D;
+    float acc = 0.f;
+    for (int d = lane; d < D; d += 32) acc = fmaf(ldf(hr + d), ldf(wr + d), acc);
+    acc = warp_sum(acc);
+    if (lane == 0) s[e] = acc;
+  }
+  __syncwarp();
+  float mx = -INFINITY;
+  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, s[e]);
+  mx = warp_max(mx);
+  float den = 0.f;
+  for (int e = lane; e < E; e += 32) den += expf(s[e] - mx);
+  den = warp_sum(den);
+  __syncwarp();
+  for (int e = lane; e < E; e += 32) s[e] = expf(s[e] - mx) / den;
+  __syncwarp();
+  if (lane == 0) {
+    // serial selection (E and top are small next to the products).  Scores are in [0, 1]; an expert of a dropped group is marked
+    // by s <- -1 - s, a chosen expert by s <- -3, so `s >= 0` means "can still be chosen".
+    const int gs = groups > 1 ? E / groups : E;
+    if (groups > 1) {
+      for (int r = 0; r < groups - keep; ++r) {                // drop the group with the smallest best score, groups - keep times
+        int worst = -1;
+        float wv = INFINITY;
+        for (int g = groups - 1; g >= 0; --g) {                // ties: the higher index is dropped first
+          if (s[(size_t)g * gs] < 0.f) continue;               // already dropped
+          float best = -1.f;
+          for (int e = 0; e < gs; ++e) best = fmaxf(best, s[(size_t)g * gs + e]);
+          if (best < wv) { wv = best; worst = g; }
+        }
+        if (worst < 0) break;
+        for (int e = 0; e < gs; ++e) s[(size_t)worst * gs + e] = -1.f - s[(size_t)worst * gs + e];
+      }
+    }
+    for (int k = 0; k < top; ++k) {
+      int bi = 0;
+      float bv = -INFINITY;
+      for (int e = 0; e < E; ++e)
+        if (s[e] >= 0.f && s[e] > bv) { bv = s[e]; bi = e; }
+      ids[(size_t)m * top + k] = bi;
+      wts[(size_t)m * top + k] = bv;
+      s[bi] = -3.f;                                            // taken
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// Mixture of experts, row form (few rows, and the 32-bit mode): every (row, chosen expert) streams that expert's matrices.
+//   moe_rows_up_kernel   act[m, k, f] = silu(W_gate[e] h_m)[f] * (W_up[e] h_m)[f],  e = ids[m, k]        one warp per f
+//   moe_rows_down_kernel y[m, d] = sum_k wts[m, k] * (W_down[e_k] act[m, k, :])[d]                       one warp per d
+// w_gu: [E][2 * F, D] (gate rows, then up rows of an expert); w_down: [E][D, F].
+// ---------------------------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void moe_rows_up_kernel(const T* __restrict__ h, int D, const T* __restrict__ w_gu, int F, const int* __restrict__ ids, int top,
+                                   T* __restrict__ act) {
+  extern __shared__ float hs[];                                // the row, fp32
+  const int m = blockIdx.x, k = blockIdx.y;
+  const int e = ids[(size_t)m * top + k];
+  for (int d = threadIdx.x; d < D; d += blockDim.x) hs[d] = ldf(h + (size_t)m * D + d);
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const T* wg = w_gu + (size_t)e * 2 * F * D;
+  const T* wu = wg + (size_t)F * D;
+  for (int f = blockIdx.z * nw + warp; f < F; f += gridDim.z * nw) {
+    float g = 0.f, u = 0.f;
+    for (int d = lane; d < D; d += 32) {
+      g = fmaf(ldf(wg + (size_t)f * D + d), hs[d], g);
+      u = fmaf(ldf(wu + (size_t)f * D + d), hs[d], u);
+    }
+    g = warp_sum(g);
+    u = warp_sum(u);
+    if (lane == 0) stf(act + ((size_t)m * top + k) * F + f, siluf_(g) * u);
+  }
+}
+template <typename T>
+__global__ void moe_rows_down_kernel(const T* __restrict__ act, int F, const T* __restrict__ w_down, int D, const int* __restrict__ ids,
+                                     const float* __restrict__ wts, int top, float* __restrict__ y) {
+  extern __shared__ float as[];                                // [top][F] fp32
+  const int m = blockIdx.x;
+  for (int i = threadIdx.x; i < top * F; i += blockDim.x) as[i] = ldf(act + (size_t)m * top * F + i);
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  for (int d = blockIdx.y * nw + warp; d < D; d += gridDim.y * nw) {
+    float out = 0.f;
+    for (int k = 0; k < top; ++k) {
+      const T* wd = w_down + ((size_t)ids[(size_t)m * top + k] * D + d) * F;
+      float acc = 0.f;
+      for (int f = lane; f < F; f += 32) acc = fmaf(ldf(wd + f), as[k * F + f], acc);
+      out = fmaf(wts[(size_t)m * top + k], warp_sum(acc), out);
+    }
+    if (lane == 0) y[(size_t)m * D + d] = out;
+  }
+}
+
+}  // namespace xl

@@ -1,0 +1,222 @@
+// layered_gqa.cuh — grouped-query attention over a paged key/value cache (mixer XOTB200_LM_MIX_ATTENTION of the layered engine).
+//
+// H query heads of size dk share G key/value heads (query head a reads key/value head a / (H / G)); values have size dv.  The cache
+// of a layer is one paged pool whose row for a token is [keys of all G heads, after their norm | values of all G heads] in T; a layer
+// may read another layer's pool (shared keys/values) with its own queries and mask.
+//
+//   score(i, j) = q_i . k_j * scale                       fp32
+//                 -> cap * tanh(score / cap)              when cap > 0
+//                 -> - r1[a] * ln(1 + r2[a] * (i - j))    when the head has a distance penalty
+//   visible     : j <= i,  i - j < window (window > 0),  floor(i / chunk) == floor(j / chunk) (chunk > 0; blocks are counted from
+//                 position 0 of the request, whatever portion of it a step brings)
+//   weights     = softmax over the visible keys (fp32), output = sum_j p_j v_j, times sigmoid(gate) per head or per entry.
+//
+// Kernels: gqa_prepare_kernel (bias, per-head RMS norm, cache append), gqa_attention_kernel + gqa_combine_kernel (one warp per
+// (row, query head); decode, short portions and the 32-bit mode), gqa_flash_kernel (tensor cores, bf16, long portions).
+#pragma once
+#include "layered_kernels.cuh"
+
+namespace xl {
+
+struct GqaScore {
+  float scale, cap;
+  int window, chunk;
+  const void* r1;    // per query head, T; NULL = no distance penalty
+  const void* r2;
+};
+
+template <typename T>
+__device__ __forceinline__ float gqa_adjust(float dot, const GqaScore& sc, float r1, float r2, int dist) {
+  float s = dot * sc.scale;
+  if (sc.cap > 0.f) s = sc.cap * tanhf(s / sc.cap);
+  if (sc.r1) s -= r1 * log1pf(r2 * (float)dist);
+  return s;
+}
+__device__ __forceinline__ bool gqa_visible(int pos, int j, int window, int chunk) {
+  return j <= pos && (window == 0 || pos - j < window) && (chunk == 0 || j / chunk == pos / chunk);
+}
+// first key any row of positions pos0 .. can see
+__device__ __host__ __forceinline__ int gqa_first_key(int pos0, int window, int chunk) {
+  int f = 0;
+  if (window > 0 && pos0 - window + 1 > f) f = pos0 - window + 1;
+  if (chunk > 0 && (pos0 / chunk) * chunk > f) f = (pos0 / chunk) * chunk;
+  return f;
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// After the input projection: proj[m, :] (fp32) holds q (H * dk) at col_q and, for a layer with keys/values of its own, k (G * dk)
+// at col_k and v (G * dv) at col_v.  Adds the projection biases, RMS-norms every query and key head over dk (weight of size dk
+// shared by the heads; w == NULL: no norm) and stores queries as fp32 [M, H, dk] (+ a bf16 copy for the tensor-core kernel) and
+// keys / values into the row's place of the paged pool.  One warp per (row, head slot): slots 0..H-1 queries, H..H+G-1 keys,
+// H+G..H+2G-1 values.
+// ---------------------------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void gqa_prepare_kernel(const float* __restrict__ proj, int ld, int col_q, int col_k, int col_v, const T* __restrict__ bias,
+                                   const T* __restrict__ q_norm, const T* __restrict__ k_norm, float eps, int H, int G, int dk, int dv, int own_kv,
+                                   const int* __restrict__ row_slot, const int* __restrict__ row_pos, Paging pg, T* __restrict__ pool,
+                                   float* __restrict__ qf, bf16* __restrict__ q16, int M) {
+  const int slots = H + (own_kv ? 2 * G : 0);
+  const int idx = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (idx >= M * slots) return;
+  const int m = idx / slots, sl = idx % slots;
+  const float* pr = proj + (size_t)m * ld;
+  if (sl >= H + G) {                                           // a value head: bias, store
+    const int g = sl - H - G, c0 = col_v + g * dv;
+    T* dst = pool + pg.row(row_slot[m], row_pos[m]) * (size_t)(G * (dk + dv)) + (size_t)G * dk + (size_t)g * dv;
+    for (int d = lane; d < dv; d += 32) stf(dst + d, pr[c0 + d] + (bias ? ldf(bias + c0 + d) : 0.f));
+    return;
+  }
+  const bool is_q = sl < H;
+  const int hd = is_q ? sl : sl - H, c0 = (is_q ? col_q : col_k) + hd * dk;
+  const T* w = is_q ? q_norm : k_norm;
+  float ss = 0.f;
+  for (int d = lane; d < dk; d += 32) { const float v = pr[c0 + d] + (bias ? ldf(bias + c0 + d) : 0.f); ss = fmaf(v, v, ss); }
+  const float rs = w ? 1.0f / sqrtf(warp_sum(ss) / (float)dk + eps) : 1.0f;
+  T* kdst = is_q ? nullptr : pool + pg.row(row_slot[m], row_pos[m]) * (size_t)(G * (dk + dv)) + (size_t)hd * dk;
+  for (int d = lane; d < dk; d += 32) {
+    const float v = (pr[c0 + d] + (bias ? ldf(bias + c0 + d) : 0.f)) * rs * (w ? ldf(w + d) : 1.f);
+    if (is_q) {
+      qf[((size_t)m * H + hd) * dk + d] = v;
+      if (q16) q16[((size_t)m * H + hd) * dk + d] = __float2bfloat16_rn(v);
+    } else {
+      stf(kdst + d, v);
+    }
+  }
+}
+
+// how the mixer output is gated: 0 none, 1 sigmoid(gate[m, col0 + head]), 2 sigmoid(gate[m, col0 + head * dv + d])
+__device__ __forceinline__ float gqa_gate(const float* gate, int mode, size_t m, int ld, int col0, int h, int dv, int d) {
+  if (mode == 0) return 1.f;
+  return sigmoidf_(gate[m * ld + col0 + (mode == 1 ? h : h * dv + d)]);
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// One CTA = one work item (up to q_per_item consecutive rows of one request) x one key/value head; one WARP owns one (row, query
+// head of the group) pair.  32 cached keys + values of the head wait in shared memory (fp32, odd row stride): lane j scores key j,
+// the softmax statistics go round by shuffles, then the lanes split the dv value columns (NACC = ceil(dv / 32) registers).
+// gridDim.z > 1: the keys are cut into runs of `chunk_keys` (a multiple of 32); run z parks {max, sum, accumulator[dv]} in `part`
+// ([M * H][gridDim.z][2 + dv]) and gqa_combine_kernel merges them.
+// ---------------------------------------------------------------------------------------------------------------------------
+template <typename T, int NACC>
+__global__ void gqa_attention_kernel(const float* __restrict__ qf, const T* __restrict__ pool, Paging pg, const Item* __restrict__ items, int H,
+                                     int G, int dk, int dv, GqaScore sc, const float* __restrict__ gate, int gate_mode, int gate_ld, int gate_col0,
+                                     T* __restrict__ out, int chunk_keys, float* __restrict__ part) {
+  extern __shared__ float smem[];
+  const Item it = items[blockIdx.x];
+  const int rep = H / G, W = dk + dv, WS = W | 1;
+  const int nw = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_y = (it.n_rows * rep + nw - 1) / nw;         // blockIdx.y = kv head * y-tiles + tile
+  const int ypg = gridDim.y / G;
+  const int g = blockIdx.y / ypg, ytile = blockIdx.y % ypg;
+  if (ytile >= tiles_y) return;                                // whole CTA: no barrier has been passed yet
+  float* ktile = smem;                                         // [32][WS]
+  float* qs = smem + 32 * WS;                                  // [warps][dk]
+  const int pair = ytile * nw + warp;
+  const bool active = pair < it.n_rows * rep;
+  const int qi = active ? pair / rep : 0, h = g * rep + (active ? pair % rep : 0);
+  const int m = it.row0 + qi, pos = it.pos0 + qi;
+  float* q = qs + (size_t)warp * dk;
+  if (active) {
+    const float* src = qf + ((size_t)m * H + h) * dk;
+    for (int d = lane; d < dk; d += 32) q[d] = src[d];
+  }
+  const float r1 = sc.r1 ? ldf(static_cast<const T*>(sc.r1) + h) : 0.f, r2 = sc.r1 ? ldf(static_cast<const T*>(sc.r2) + h) : 0.f;
+  int last = it.pos0 + it.n_rows - 1;
+  int first = gqa_first_key(it.pos0, sc.window, sc.chunk);
+  if (gridDim.z > 1) {
+    first += blockIdx.z * chunk_keys;
+    last = min(last, first + chunk_keys - 1);
+  }
+  float acc[NACC];
+#pragma unroll
+  for (int a = 0; a < NACC; ++a) acc[a] = 0.f;
+  float mx = -INFINITY, den = 0.f;
+  const size_t rowlen = (size_t)G * W;
+  for (int j0 = first; j0 <= last; j0 += 32) {
+    __syncthreads();
+    for (int jr = warp; jr < 32; jr += nw) {
+      const int j = j0 + jr;
+      float* dst = ktile + jr * WS;
+      if (j <= last) {
+        const T* src = pool + pg.row(it.slot, j) * rowlen;
+        for (int d = lane; d < dk; d += 32) dst[d] = ldf(src + (size_t)g * dk + d);
+        for (int d = lane; d < dv; d += 32) dst[dk + d] = ldf(src + (size_t)G * dk + (size_t)g * dv + d);
+      } else {
+        for (int d = lane; d < W; d += 32) dst[d] = 0.f;
+      }
+    }
+    __syncthreads();
+    if (!active) continue;
+    const int j = j0 + lane;
+    const bool vis = j <= last && gqa_visible(pos, j, sc.window, sc.chunk);
+    float s = 0.f;
+    const float* kr = ktile + lane * WS;
+    for (int d = 0; d < dk; ++d) s = fmaf(q[d], kr[d], s);
+    s = vis ? gqa_adjust<T>(s, sc, r1, r2, pos - j) : -INFINITY;
+    const float tmax = warp_max(s);
+    if (tmax == -INFINITY) continue;                           // warp-uniform
+    const float nmx = fmaxf(mx, tmax);
+    const float corr = expf(mx - nmx);
+    const float p = vis ? expf(s - nmx) : 0.f;
+    den = den * corr + warp_sum(p);
+    mx = nmx;
+#pragma unroll
+    for (int a = 0; a < NACC; ++a) acc[a] *= corr;
+    for (int jr = 0; jr < 32; ++jr) {
+      const float pj = __shfl_sync(0xffffffffu, p, jr);
+      if (pj == 0.f) continue;                                 // warp-uniform
+      const float* v = ktile + jr * WS + dk;
+#pragma unroll
+      for (int a = 0; a < NACC; ++a) {
+        const int d = a * 32 + lane;
+        if (d < dv) acc[a] = fmaf(pj, v[d], acc[a]);
+      }
+    }
+  }
+  if (!active) return;
+  if (gridDim.z > 1) {
+    float* dst = part + (((size_t)m * H + h) * gridDim.z + blockIdx.z) * (size_t)(2 + dv);
+    if (lane == 0) { dst[0] = mx; dst[1] = den; }
+#pragma unroll
+    for (int a = 0; a < NACC; ++a) {
+      const int d = a * 32 + lane;
+      if (d < dv) dst[2 + d] = acc[a];
+    }
+    return;
+  }
+  const float inv = 1.0f / den;
+  T* o = out + (size_t)m * H * dv + (size_t)h * dv;
+#pragma unroll
+  for (int a = 0; a < NACC; ++a) {
+    const int d = a * 32 + lane;
+    if (d < dv) stf(o + d, acc[a] * inv * gqa_gate(gate, gate_mode, m, gate_ld, gate_col0, h, dv, d));
+  }
+}
+
+// merges the key runs: one warp per (row, query head) of the listed items; at most 32 runs
+template <typename T>
+__global__ void gqa_combine_kernel(const float* __restrict__ part, const Item* __restrict__ items, int H, int dv, int splits,
+                                   const float* __restrict__ gate, int gate_mode, int gate_ld, int gate_col0, T* __restrict__ out) {
+  const Item it = items[blockIdx.x];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const int pair = blockIdx.y * nw + warp;
+  if (pair >= it.n_rows * H) return;
+  const int m = it.row0 + pair / H, h = pair % H;
+  const float* src = part + ((size_t)m * H + h) * splits * (size_t)(2 + dv);
+  const float mz = lane < splits ? src[(size_t)lane * (2 + dv)] : -INFINITY;
+  const float mx = warp_max(mz);
+  const float wz = mz == -INFINITY ? 0.f : expf(mz - mx);
+  const float den = warp_sum(lane < splits ? src[(size_t)lane * (2 + dv) + 1] * wz : 0.f);
+  const float inv = 1.0f / den;
+  for (int d0 = 0; d0 < dv; d0 += 32) {
+    const int d = d0 + lane;
+    float a = 0.f;
+    for (int z = 0; z < splits; ++z) {
+      const float w = __shfl_sync(0xffffffffu, wz, z);
+      if (w != 0.f && d < dv) a = fmaf(src[(size_t)z * (2 + dv) + 2 + d], w, a);
+    }
+    if (d < dv) stf(out + (size_t)m * H * dv + (size_t)h * dv + d, a * inv * gqa_gate(gate, gate_mode, m, gate_ld, gate_col0, h, dv, d));
+  }
+}
+
+}  // namespace xl

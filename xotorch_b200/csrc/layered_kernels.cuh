@@ -36,6 +36,12 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 __device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf(-z)); }
+__device__ __forceinline__ float softplusf_(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+__device__ __forceinline__ float siluf_(float z) { return z / (1.0f + expf(-z)); }
+// xIELU:  z > 0: softplus(p) z^2 + z / 2;   z <= 0: (1/2 + softplus(q)) (e^z - 1 - z) + z / 2.   ap = softplus(p), aq = 1/2 + softplus(q).
+__device__ __forceinline__ float xielu_f(float z, float ap, float aq) {
+  return z > 0.f ? fmaf(ap * z, z, 0.5f * z) : fmaf(aq, expm1f(z) - z, 0.5f * z);
+}
 
 // Where a request's token lives in a paged pool: page_table[slot * pages_per_slot + pos / P] * P + pos % P.
 struct Paging {
@@ -383,11 +389,17 @@ __device__ __forceinline__ void cp_async16(float* dst_smem, const float* src) {
 // A thread owns NC value columns x KPT key rows of the state (row i = e * P + part), so the token's vectors, read from shared
 // memory once, serve NC columns and the NC recurrences run as independent chains.  vec4: every source row is 16-byte aligned
 // (sizes and offsets multiples of 4 floats), so the staging uses 16-byte cp.async.
+// The write key k, the read-out vector r and the value v each come from their own fp32 matrix (pointer, leading dimension, first
+// column; head a's vector at column a * dk, resp. a * dv): a projection output or a prepared buffer.
+struct DeltaSrc {
+  const float* p;
+  int ld, col;
+};
 template <int KPT, int P, int NC>
-__global__ void delta_rule_kernel(const float* __restrict__ proj, int ld, int col_r, int col_k, int col_v, const float* __restrict__ wdec,
+__global__ void delta_rule_kernel(DeltaSrc ksrc, DeltaSrc rsrc, DeltaSrc vsrc, const float* __restrict__ wdec,
                                   const float* __restrict__ uvec, const float* __restrict__ auvec, const Item* __restrict__ seqs, int H, int dk,
                                   int dv, float* __restrict__ state, size_t state_slot_stride, float* __restrict__ o_raw, int vec4) {
-  constexpr int DKP = KPT * P;                       // padded key size (>= dk, and >= dv: the design uses one size for both)
+  constexpr int DKP = KPT * P;                       // padded size: >= dk and >= dv
   constexpr int CH = DKP <= 64 ? 16 : DKP <= 128 ? 8 : 4;   // tokens per buffer: two buffers fill the 48 KB of static shared memory
   __shared__ __align__(16) float buf[2][CH][6][DKP]; // per token: w, a*u, u, k, r, v
   const Item sq = seqs[blockIdx.x / H];
@@ -409,16 +421,17 @@ __global__ void delta_rule_kernel(const float* __restrict__ proj, int ld, int co
   const int HD = H * dk;
   auto issue = [&](int c) {
     const int t0 = c * CH, nt = min(CH, sq.n_rows - t0);
-    const int per = vec4 ? dk / 4 : dk;              // copies per vector
-    for (int e = threadIdx.x; e < nt * 6 * per; e += blockDim.x) {
-      const int t = e / (6 * per), rem = e % (6 * per), vec = rem / per, i = (rem % per) * (vec4 ? 4 : 1);
+    const int perk = vec4 ? dk / 4 : dk, perv = vec4 ? dv / 4 : dv;   // copies per key-sized vector / per value vector
+    const int per_tok = 5 * perk + perv;
+    for (int e = threadIdx.x; e < nt * per_tok; e += blockDim.x) {
+      const int t = e / per_tok, rem = e % per_tok, vec = rem / perk < 5 ? rem / perk : 5, i = (rem - vec * perk) * (vec4 ? 4 : 1);
       const size_t m = (size_t)sq.row0 + t0 + t;
       const float* src = vec == 0 ? wdec + m * HD + h * dk + i
                        : vec == 1 ? auvec + m * HD + h * dk + i
                        : vec == 2 ? uvec + m * HD + h * dk + i
-                       : vec == 3 ? proj + m * ld + col_k + h * dk + i
-                       : vec == 4 ? proj + m * ld + col_r + h * dk + i
-                                  : proj + m * ld + col_v + h * dv + i;
+                       : vec == 3 ? ksrc.p + m * ksrc.ld + ksrc.col + h * dk + i
+                       : vec == 4 ? rsrc.p + m * rsrc.ld + rsrc.col + h * dk + i
+                                  : vsrc.p + m * vsrc.ld + vsrc.col + h * dv + i;
       if (vec4) cp_async16(&buf[c & 1][t][vec][i], src);
       else cp_async4(&buf[c & 1][t][vec][i], src);
     }
@@ -483,9 +496,11 @@ __global__ void delta_rule_kernel(const float* __restrict__ proj, int ld, int co
 }
 
 // Output side of the delta-rule mixer: per (row, head) o / rms(o) * w_norm * sigmoid(gate) -> T, the operand of the output product.
+// w_head_stride: dv when every head has its own norm weight, 0 when the heads share one of size dv.  gate_silu: 0 = sigmoid(gate),
+// 1 = silu(gate).
 template <typename T>
-__global__ void head_norm_gate_kernel(const float* __restrict__ o_raw, const T* __restrict__ w_norm, const float* __restrict__ gate, int gate_ld,
-                                      int gate_col0, T* __restrict__ out, int H, int dv, float eps, int M) {
+__global__ void head_norm_gate_kernel(const float* __restrict__ o_raw, const T* __restrict__ w_norm, int w_head_stride, const float* __restrict__ gate,
+                                      int gate_ld, int gate_col0, int gate_silu, T* __restrict__ out, int H, int dv, float eps, int M) {
   const int idx = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (idx >= M * H) return;
   const int m = idx / H, h = idx % H;
@@ -493,9 +508,10 @@ __global__ void head_norm_gate_kernel(const float* __restrict__ o_raw, const T* 
   float s = 0.f;
   for (int d = lane; d < dv; d += 32) s = fmaf(o[d], o[d], s);
   const float rs = 1.0f / sqrtf(warp_sum(s) / (float)dv + eps);
-  for (int d = lane; d < dv; d += 32)
-    stf(out + (size_t)m * H * dv + (size_t)h * dv + d,
-        o[d] * rs * ldf(w_norm + h * dv + d) * sigmoidf_(gate[(size_t)m * gate_ld + gate_col0 + h * dv + d]));
+  for (int d = lane; d < dv; d += 32) {
+    const float z = gate[(size_t)m * gate_ld + gate_col0 + h * dv + d];
+    stf(out + (size_t)m * H * dv + (size_t)h * dv + d, o[d] * rs * ldf(w_norm + h * w_head_stride + d) * (gate_silu ? z * sigmoidf_(z) : sigmoidf_(z)));
+  }
 }
 
 // out[m, :n] = tanh(in[m, col0 : col0 + n])  (fp32 in, T out): the low-rank decay branch between its two products
@@ -510,13 +526,13 @@ __global__ void tanh_cols_kernel(const float* __restrict__ in, int ld, int col0,
 // ---------------------------------------------------------------------------------------------------------------------------
 // Products.  C[z][m, n] = sum_k A[z][m, k] * B[z][n, k]   with fp32 accumulation; A row-major (lda), B addressed by two strides
 // (sbn, sbk) so that a weight stored [K, N] is used without a transposed copy, z = batch (per-head products) via element offsets.
-// EPI 1: C = relu(C)^2.
+// EPI 1: C = relu(C)^2.  EPI 2: C = xIELU(C) with the two raw parameters p, q at `epi` (in the weights' type).
 // gemm_tiled_kernel: 64 x 64 x 16 shared-memory tiles, 256 threads, 4 x 4 outputs per thread, fp32 FMA (exact fp32 in the 32-bit mode).
 // ---------------------------------------------------------------------------------------------------------------------------
 template <typename TA, typename TB, typename TC, int EPI>
 __global__ void __launch_bounds__(256)
 gemm_tiled_kernel(const TA* __restrict__ A, long lda, long a_batch, const TB* __restrict__ B, long sbn, long sbk, long b_batch, TC* __restrict__ C,
-                  long ldc, long c_batch, int M, int N, int K) {
+                  long ldc, long c_batch, int M, int N, int K, const TB* __restrict__ epi) {
   constexpr int BM = 64, BN = 64, BK = 16;
   __shared__ float As[BK][BM + 4], Bs[BK][BN + 4];
   A += (size_t)blockIdx.z * a_batch;
@@ -556,6 +572,8 @@ gemm_tiled_kernel(const TA* __restrict__ A, long lda, long a_batch, const TB* __
     }
     __syncthreads();
   }
+  float ap = 0.f, aq = 0.f;
+  if (EPI == 2) { ap = softplusf_(ldf(epi)); aq = 0.5f + softplusf_(ldf(epi + 1)); }
 #pragma unroll
   for (int i = 0; i < 4; ++i)
 #pragma unroll
@@ -564,6 +582,7 @@ gemm_tiled_kernel(const TA* __restrict__ A, long lda, long a_batch, const TB* __
       if (m < M && n < N) {
         float v = acc[i][j];
         if (EPI == 1) { v = fmaxf(v, 0.f); v *= v; }
+        if (EPI == 2) v = xielu_f(v, ap, aq);
         stf(C + (size_t)m * ldc + n, v);
       }
     }
@@ -576,7 +595,7 @@ gemm_tiled_kernel(const TA* __restrict__ A, long lda, long a_batch, const TB* __
 template <typename TA, typename TB, typename TC, int EPI, int MR>
 __global__ void __launch_bounds__(256)
 gemv_rows_kernel(const TA* __restrict__ A, long lda, long a_batch, const TB* __restrict__ B, long sbn, long b_batch, TC* __restrict__ C, long ldc,
-                 long c_batch, int M, int N, int K, int wsplit) {
+                 long c_batch, int M, int N, int K, int wsplit, const TB* __restrict__ epi) {
   constexpr int RB = 4;
   extern __shared__ float a_s[];                     // [M][K], then the slice sums [8 warps][RB][MR]
   A += (size_t)blockIdx.z * a_batch;
@@ -652,6 +671,7 @@ gemv_rows_kernel(const TA* __restrict__ A, long lda, long a_batch, const TB* __r
       for (int sidx = 0; sidx < wsplit; ++sidx) v += red[((warp + sidx) * RB + r) * MR + m];   // fixed order: deterministic
       if (m < M && n0 + r < N) {
         if (EPI == 1) { v = fmaxf(v, 0.f); v *= v; }
+        if (EPI == 2) v = xielu_f(v, softplusf_(ldf(epi)), 0.5f + softplusf_(ldf(epi + 1)));
         stf(C + (size_t)m * ldc + n0 + r, v);
       }
     }

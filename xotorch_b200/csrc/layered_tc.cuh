@@ -10,6 +10,7 @@
 // (plain row-major weights, batched per-head products through the third coordinate), the epilogue and that EVERY wait is bounded:
 // a wait that expires sets *err and the CTA drains, frees its tensor memory and returns.
 #pragma once
+#include "layered_kernels.cuh"
 #include "prefill_tc.cuh"
 
 namespace xl {
@@ -36,6 +37,7 @@ struct LtcArgs {
   void* C;          // fp32 or bf16 [*, ldc]
   long ldc, c_batch;
   int* err;
+  const __nv_bfloat16* epi;   // EPI 2: the two raw xIELU parameters
 };
 
 template <typename TC>
@@ -112,6 +114,8 @@ ltc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       TC* crow = static_cast<TC*>(a.C) + (size_t)z * a.c_batch + (size_t)row * a.ldc;
       const bool vec = (sizeof(TC) == 4) && ((a.ldc | a.c_batch) % 4 == 0) && ((reinterpret_cast<uintptr_t>(a.C) & 15) == 0);
       const bool vec16 = (sizeof(TC) == 2) && ((a.ldc | a.c_batch) % 8 == 0) && ((reinterpret_cast<uintptr_t>(a.C) & 15) == 0);
+      float ap = 0.f, aq = 0.f;
+      if (EPI == 2) { ap = softplusf_(__bfloat162float(a.epi[0])); aq = 0.5f + softplusf_(__bfloat162float(a.epi[1])); }
 #pragma unroll 1
       for (int c0 = 0; c0 < NT; c0 += 16) {
         uint32_t v[16];
@@ -123,6 +127,7 @@ ltc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         for (int j = 0; j < 16; ++j) {
           f[j] = __uint_as_float(v[j]);
           if (EPI == 1) { f[j] = fmaxf(f[j], 0.f); f[j] *= f[j]; }
+          if (EPI == 2) f[j] = xielu_f(f[j], ap, aq);
         }
         if (vec && n + 16 <= a.N) {
           float4* d4 = reinterpret_cast<float4*>(reinterpret_cast<float*>(crow) + n);

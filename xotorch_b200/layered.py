@@ -41,6 +41,20 @@ class LayerSpec:
   ff: int = 0
   rot_base: float = 10000.0
   scale: float = 1.0
+  kv_heads: int = 0
+  kv_from: int = -1
+  chunk: int = 0
+  qk_norm: int = 0
+  proj_bias: int = 0
+  dist_bias: int = 0
+  conv_taps: int = 0
+  ff_kind: int = _lib.LM_FF_RELU2
+  experts: int = 0
+  expert_ff: int = 0
+  top: int = 0
+  groups: int = 0
+  groups_keep: int = 0
+  softcap: float = 0.0
 
   def to_c(self) -> LmLayer:
     c = LmLayer()
@@ -108,7 +122,54 @@ def zokuvik_globals(config: dict) -> dict:
               norm_eps=float(config["norm"]["eps"]))
 
 
-LAYERED_FAMILIES = {"Zokuvik": (zokuvik_layers, zokuvik_globals)}
+# ---- the Bufulorn family -----------------------------------------------------------------------------------------------------
+# config.json: {"architecture": "Bufulorn", "width", "vocab", "max_positions", "norm": {"eps"}, "layers": [{"type", "mixer", "mlp"}]}
+# A layer is x += LN(mixer(x)), x += LN(ff(x)) (layer norms with weight and bias on the sublayers' outputs); a learned position
+# vector is added to the embedding.
+#   type "attention"  grouped-query attention (mixer: heads, kv_heads, dim, vdim, scale, softcap, mask.size = block of the
+#                     block-local causal mask, kv_from = layer whose keys/values it reads): biased projections, per-head RMS norm of
+#                     queries and keys, logarithmic distance penalty, no rotation, one sigmoid gate per output entry
+#   type "delta"      gated delta rule (mixer: heads, kv_heads, dim, vdim, conv = taps of the short convolutions)
+#   mlp.kind "dense"  W_down xIELU(W_up h) (mlp.ff);  "moe": mlp.router {experts, top, groups {count, keep}}, mlp.expert.ff
+def _bufulorn_ff(i: int, mlp) -> dict:
+  if mlp is None:
+    return dict(ff=0, ff_kind=_lib.LM_FF_XIELU)
+  kind = mlp.get("kind", "dense")
+  if kind == "dense":
+    return dict(ff=int(mlp["ff"]), ff_kind=_lib.LM_FF_XIELU)
+  if kind == "moe":
+    r = mlp["router"]
+    groups = r.get("groups") or {}
+    return dict(ff=0, ff_kind=_lib.LM_FF_MOE, experts=int(r["experts"]), top=int(r["top"]), expert_ff=int(mlp["expert"]["ff"]),
+                groups=int(groups.get("count", 0)), groups_keep=int(groups.get("keep", groups.get("count", 0))))
+  raise ValueError(f"layer {i}: feed-forward kind {kind!r} is not implemented (dense, moe)")
+
+
+def bufulorn_layers(config: dict, shapes: Dict[str, Tuple[int, ...]]) -> List[LayerSpec]:
+  out = []
+  for i, layer in enumerate(config["layers"]):
+    kind, m = layer["type"], layer["mixer"]
+    ff = _bufulorn_ff(i, layer.get("mlp"))
+    if kind == "attention":
+      src = m.get("kv_from")
+      out.append(LayerSpec(
+        mixer=_lib.LM_MIX_ATTENTION, heads=int(m["heads"]), kv_heads=int(m.get("kv_heads", m["heads"])), dim=int(m["dim"]), vdim=int(m["vdim"]),
+        scale=float(m["scale"]), softcap=float(m.get("softcap") or 0.0), chunk=int((m.get("mask") or {}).get("size", 0)),
+        kv_from=-1 if src is None else int(src), qk_norm=1, proj_bias=1, dist_bias=1, out_gate=2, **ff))
+    elif kind == "delta":
+      out.append(LayerSpec(mixer=_lib.LM_MIX_GATED_DELTA, heads=int(m["heads"]), kv_heads=int(m.get("kv_heads", m["heads"])), dim=int(m["dim"]),
+                           vdim=int(m["vdim"]), conv_taps=int(m["conv"]), **ff))
+    else:
+      raise ValueError(f"layer {i}: mixer type {kind!r} is not implemented")
+  return out
+
+
+def bufulorn_globals(config: dict) -> dict:
+  return dict(width=int(config["width"]), vocab=int(config["vocab"]), norm_groups=1, norm_eps=float(config["norm"]["eps"]),
+              block=_lib.LM_BLOCK_POST_LN, max_positions=int(config["max_positions"]))
+
+
+LAYERED_FAMILIES = {"Zokuvik": (zokuvik_layers, zokuvik_globals), "Bufulorn": (bufulorn_layers, bufulorn_globals)}
 
 
 class LayeredShard:
@@ -158,6 +219,7 @@ class LayeredShard:
     cfg.n_layers, cfg.start_layer, cfg.end_layer = self.n_layers, int(start_layer), int(end_layer)
     cfg.width, cfg.vocab, cfg.norm_groups = self.globals["width"], self.globals["vocab"], self.globals["norm_groups"]
     cfg.norm_eps = self.globals["norm_eps"]
+    cfg.block, cfg.max_positions = self.globals.get("block", _lib.LM_BLOCK_GROUP_RMS), self.globals.get("max_positions", 0)
     cfg.dtype = _lib.LM_DTYPE_F32 if self.dtype == "float32" else _lib.LM_DTYPE_BF16
     arr = (LmLayer * len(specs))(*[s.to_c() for s in specs])
     h = C.c_void_p()

@@ -30,8 +30,8 @@ def model_summary(config: dict) -> dict:
   if is_layered(config):
     from .layered import LAYERED_FAMILIES
     g = LAYERED_FAMILIES[config["architecture"]][1](config)
-    return {"n_layers": len(config["layers"]), "vocab": g["vocab"], "width": g["width"], "max_positions": NO_CONTEXT_LIMIT,
-            "engine": "layered"}
+    return {"n_layers": len(config["layers"]), "vocab": g["vocab"], "width": g["width"],
+            "max_positions": g.get("max_positions") or NO_CONTEXT_LIMIT, "engine": "layered"}
   if "num_hidden_layers" in config:
     return {"n_layers": int(config["num_hidden_layers"]), "vocab": int(config["vocab_size"]), "width": int(config["hidden_size"]),
             "max_positions": int(config.get("max_position_embeddings", NO_CONTEXT_LIMIT)), "engine": "shard"}
