@@ -1,0 +1,449 @@
+"""The Bufulorn family on the layered engine (libxotb200_lm.so) against the plain oracle (tests/bufulorn_oracle.py) on small random
+models (-m gpu).  The float32 engine is held to the oracle in float64 tightly, the bfloat16 engine loosely; tests ask for the
+logits of EVERY row unless they say otherwise, so a wrong key, block edge, filter input or state at any place shows."""
+import json
+import struct
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from tests import bufulorn_oracle as bo
+from tests.bufulorn_util import attention, config, delta, dense, moe, oracle_logits
+from tests.layered_util import TOL, bf16_bits, make_engine, rand_tokens, row_err, run_cut
+
+DTYPES = ["float32", "bfloat16"]
+
+# attention with its own keys/values, a layer that borrows them, both feed-forward kinds, two delta layers of different shapes
+MIXED = [delta(heads=4, kv_heads=2, dim=8, vdim=6, conv=4, mlp=dense(40)),
+         attention(heads=4, kv_heads=2, dim=8, vdim=12, chunk=16, mlp=moe(8, 2, (4, 2), 12)),
+         attention(heads=4, kv_heads=2, dim=8, vdim=12, chunk=7, softcap=5.0, kv_from=1, mlp=dense(24)),
+         delta(heads=3, kv_heads=3, dim=12, vdim=20, conv=2, mlp=moe(6, 3, None, 10)),
+         attention(heads=3, kv_heads=1, dim=10, vdim=5, chunk=None, softcap=None, mlp=None)]
+
+
+def check(native, cfg, W, tokens, cuts, dtype, slot=0, tol=None):
+  ref, _ = oracle_logits(cfg, W, tokens)
+  got = run_cut(native, slot, tokens, cuts)
+  e = row_err(got, ref)
+  assert e < (tol or TOL[dtype]), f"{dtype}: rows differ from the oracle, worst relative error {e:.3e}"
+  return got
+
+
+# ---- each mechanism alone ------------------------------------------------------------------------------------------------
+SINGLE = {
+  "attention_blocks": [attention(chunk=8)],
+  "attention_block_of_one": [attention(chunk=1)],
+  "attention_unmasked_uncapped": [attention(chunk=None, softcap=None)],
+  "attention_one_kv_head": [attention(heads=6, kv_heads=1, dim=8, vdim=8, chunk=11)],
+  "attention_all_kv_heads": [attention(heads=5, kv_heads=5, dim=6, vdim=7, chunk=33)],
+  "attention_odd_sizes": [attention(heads=3, kv_heads=3, dim=5, vdim=3, chunk=13, softcap=2.5)],
+  "attention_wide_values": [attention(heads=2, kv_heads=1, dim=40, vdim=72, chunk=20)],
+  "attention_many_heads": [attention(heads=40, kv_heads=8, dim=4, vdim=4, chunk=9)],
+  "attention_borrowed_keys": [attention(heads=4, kv_heads=2, chunk=16), attention(heads=4, kv_heads=2, chunk=5, softcap=None, kv_from=0)],
+  "delta": [delta()],
+  "delta_one_tap": [delta(conv=1)],
+  "delta_seven_taps": [delta(heads=2, kv_heads=1, dim=16, vdim=16, conv=7)],
+  "delta_wide_values": [delta(heads=2, kv_heads=2, dim=8, vdim=40, conv=3)],
+  "delta_wide_keys": [delta(heads=3, kv_heads=1, dim=72, vdim=12, conv=4)],
+  "delta_odd_sizes": [delta(heads=6, kv_heads=2, dim=5, vdim=7, conv=2)],
+  "dense_ff": [attention(chunk=4, mlp=dense(50))],
+  "experts_in_groups": [attention(chunk=4, mlp=moe(12, 3, (4, 2), 9))],
+  "experts_no_groups_top_1": [delta(mlp=moe(5, 1, None, 16))],
+  "experts_all_chosen": [delta(mlp=moe(4, 4, (2, 2), 8))],
+  "experts_one_group_kept": [attention(chunk=6, mlp=moe(9, 2, (3, 1), 8))],
+}
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", sorted(SINGLE))
+def test_one_mechanism_models(name, dtype):
+  cfg = config(SINGLE[name], width=36 if "odd" in name else 48)
+  W = bo.random_weights(cfg, 11)
+  n = make_engine(cfg, W, dtype)
+  toks = rand_tokens(cfg["vocab"], 41, 3)
+  n.set_trace(True)
+  ref, trail = oracle_logits(cfg, W, toks)
+  got, _ = n.step([0], [toks], want=list(range(len(toks))))
+  x = n.read_trace(len(toks))
+  for i, t in enumerate(trail):
+    assert np.abs(x[i] - t).max() / np.abs(t).max() < (1e-5 if dtype == "float32" else 0.03), f"residual stream after layer {i} differs"
+  assert row_err(got, ref) < TOL[dtype]
+  n.set_trace(False)
+  cut = run_cut(n, 1, toks, [7, 5, 1])               # short portions and single rows: state and cache carried between steps
+  assert row_err(cut, ref) < TOL[dtype]
+  n.close()
+
+
+# ---- prefill / decoding / portions -----------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("cuts", [[1], [2], [3], [17, 1], [5, 2, 9, 1], [64]])
+def test_portions_equal_the_whole_prompt(cuts, dtype):
+  cfg = config(MIXED)
+  W = bo.random_weights(cfg, 2)
+  n = make_engine(cfg, W, dtype, page_size=4)
+  toks = rand_tokens(cfg["vocab"], 37, 8)
+  got = check(n, cfg, W, toks, cuts, dtype)
+  n.clear_request(0)
+  whole = run_cut(n, 0, toks, [len(toks)])
+  assert row_err(got, whole.astype(np.float64)) < (2e-5 if dtype == "float32" else 0.05), "cutting the prompt changes rounding only"
+  n.close()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding(dtype):
+  cfg = config([attention(chunk=33, mlp=dense(32)), delta(heads=2, kv_heads=1, dim=16, vdim=8, mlp=moe(4, 2, (2, 1), 8)),
+                attention(heads=2, kv_heads=2, dim=8, vdim=8, chunk=None, kv_from=None)], width=32)
+  W = bo.random_weights(cfg, 21)
+  n = make_engine(cfg, W, dtype, max_tokens=400, page_size=16)
+  check(n, cfg, W, rand_tokens(cfg["vocab"], 300, 4), [6, 1], dtype)
+  n.close()
+
+
+def test_first_tokens_of_a_sequence():
+  cfg = config(MIXED)
+  W = bo.random_weights(cfg, 9)
+  n = make_engine(cfg, W, "float32")
+  for length in (1, 2, 3, 5):
+    n.clear_request(0)
+    check(n, cfg, W, rand_tokens(cfg["vocab"], length, length), [1], "float32")
+    n.clear_request(0)
+    check(n, cfg, W, rand_tokens(cfg["vocab"], length, length), [length], "float32")
+  n.close()
+
+
+def test_position_table_bounds_a_request():
+  cfg = config([attention(chunk=4)], max_positions=12)
+  W = bo.random_weights(cfg, 1)
+  n = make_engine(cfg, W, "float32")
+  check(n, cfg, W, rand_tokens(cfg["vocab"], 12, 1), [5], "float32")
+  with pytest.raises(Exception, match="positions"):
+    n.step([0], [rand_tokens(cfg["vocab"], 1, 2)])
+  n.close()
+
+
+# ---- batches ---------------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_unequal_requests_in_one_batch_equal_each_alone(dtype):
+  cfg = config(MIXED)
+  W = bo.random_weights(cfg, 4)
+  n = make_engine(cfg, W, dtype, max_tokens=256, max_requests=5, page_size=4)
+  lens = [1, 13, 30, 2, 8]
+  seqs = [rand_tokens(cfg["vocab"], L + 6, 50 + i) for i, L in enumerate(lens)]
+  refs = [oracle_logits(cfg, W, s)[0] for s in seqs]
+  slots = [3, 0, 4, 1, 2]
+  lg, _ = n.step(slots, [s[:L] for s, L in zip(seqs, lens)], want=list(range(sum(lens))))
+  at = 0
+  for i, L in enumerate(lens):
+    assert row_err(lg[at:at + L], refs[i][:L]) < TOL[dtype], f"prompt of request {i}"
+    at += L
+  live = list(range(len(lens)))
+  for t in range(6):
+    if t == 2:
+      live.remove(0)
+      n.clear_request(slots[0])
+    if t == 4:
+      live.remove(3)
+      n.clear_request(slots[3])
+    lg, am = n.step([slots[i] for i in live], [seqs[i][lens[i] + t:lens[i] + t + 1] for i in live])
+    for k, i in enumerate(live):
+      assert row_err(lg[k:k + 1], refs[i][lens[i] + t:lens[i] + t + 1]) < TOL[dtype], f"request {i}, decoded token {t}"
+      assert am[k] == int(np.argmax(lg[k]))
+  n.close()
+
+
+def test_mixed_batch_of_portions_and_decoded_rows():
+  cfg = config(MIXED)
+  W = bo.random_weights(cfg, 6)
+  n = make_engine(cfg, W, "float32", page_size=4)
+  a, b = rand_tokens(cfg["vocab"], 20, 1), rand_tokens(cfg["vocab"], 26, 2)
+  ra, rb = oracle_logits(cfg, W, a)[0], oracle_logits(cfg, W, b)[0]
+  n.step([0], [a[:15]])
+  lg, _ = n.step([0, 1], [a[15:16], b[:11]], want=list(range(12)))
+  assert row_err(lg[:1], ra[15:16]) < TOL["float32"] and row_err(lg[1:], rb[:11]) < TOL["float32"]
+  lg, _ = n.step([1, 0], [b[11:26], a[16:17]], want=list(range(16)))
+  assert row_err(lg[:15], rb[11:26]) < TOL["float32"] and row_err(lg[15:], ra[16:17]) < TOL["float32"]
+  n.close()
+
+
+# ---- pages, slots and states that are given back and used again --------------------------------------------------------------
+def test_freed_pages_slots_and_states_are_clean_for_the_next_request():
+  cfg = config(MIXED)
+  W = bo.random_weights(cfg, 13)
+  n = make_engine(cfg, W, "float32", max_tokens=64, max_requests=2, page_size=4)
+  total = n.cache_stats()["pages_total"]
+  a, b, c = (rand_tokens(cfg["vocab"], L, s) for L, s in ((29, 1), (18, 2), (31, 3)))
+  check(n, cfg, W, a, [9, 1], "float32", slot=0)
+  check(n, cfg, W, b, [18], "float32", slot=1)
+  assert n.cache_stats()["pages_free"] == total - 8 - 5
+  n.clear_request(0)                                  # a's pages, recurrent states and filter inputs go back ...
+  assert n.cache_stats()["pages_free"] == total - 5 and n.request_len(0) == 0
+  check(n, cfg, W, c, [5, 3, 1], "float32", slot=0)   # ... and c starts clean on them, next to the live b
+  lg, _ = n.step([1], [a[:3]], want=[0, 1, 2])        # b goes on undisturbed
+  ref = oracle_logits(cfg, W, np.concatenate([b, a[:3]]))[0]
+  assert row_err(lg, ref[18:]) < TOL["float32"]
+  n.clear_request(0)
+  n.clear_request(1)
+  assert n.cache_stats()["pages_free"] == total
+  with pytest.raises(Exception, match="cache"):
+    n.step([0], [rand_tokens(cfg["vocab"], 200, 1)])
+  assert n.cache_stats()["pages_free"] == total and n.request_len(0) == 0
+  n.close()
+
+
+# ---- keys that must (not) be seen: made to stand out -------------------------------------------------------------------------
+def plant(cfg, W):
+  """The last two tokens of the vocabulary get embeddings made for each other: the key of the first and every query of the second
+  point along one sign vector (the projections are inverted for it), so that this pair's score stands out from all others."""
+  m, V = cfg["layers"][0]["mixer"], cfg["vocab"]
+  u = torch.tensor([1.0, -1.0] * (m["dim"] // 2), dtype=torch.float64)
+  W["embed"][V - 2] = (4.0 * torch.linalg.pinv(W["l0.mix.k"].double()) @ u.repeat(m["kv_heads"])).float()
+  W["embed"][V - 1] = (torch.linalg.pinv(W["l0.mix.q"].double()) @ u.repeat(m["heads"])).float()
+  W["embed"] = W["embed"].to(torch.bfloat16).to(torch.float32)
+  return V - 2, V - 1
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("decode", [False, True])
+def test_block_edges_and_far_keys(decode, dtype):
+  """One key made to take nearly all the weight of the last row (sharp scores, planted embeddings): a far key and a key at a page
+  border of an unmasked mixer, the first key of the last row's block, and the last key of the block before it (which must NOT be
+  seen).  Reading one key too many or too few moves the logits by far more than the tolerance.  The block edge lies inside the
+  decoded part when `decode`."""
+  V, n_tok, block = 40, 150, 23
+  last = n_tok - 1
+  edge = (last // block) * block                      # first position of the last row's block
+  assert n_tok - 40 < edge < last
+  cases = [("far", None, 3, None), ("page_border", None, 64, None), ("block_in", block, edge, None), ("block_out", block, edge - 1, last + 1)]
+  for name, size, pos, seen_with in cases:
+    layer = attention(heads=2, kv_heads=1, dim=16, vdim=12, scale=2.0, softcap=None, chunk=size)
+    cfg = config([layer], vocab=V, width=64)
+    W = bo.random_weights(cfg, 17)
+    W["l0.mix.r1"] = (0.2 * W["l0.mix.r1"]).to(torch.bfloat16).to(torch.float32)   # a mild distance penalty: a far key can still dominate
+    key_tok, query_tok = plant(cfg, W)
+    seq = rand_tokens(V - 2, n_tok, 5)
+    seq[-1] = query_tok
+    without = oracle_logits(cfg, W, seq)[0]
+    seq[pos] = key_tok
+    seen_cfg = config([layer], vocab=V, width=64)
+    if seen_with:
+      seen_cfg["layers"][0]["mixer"]["mask"]["size"] = seen_with     # what the key WOULD do if the mask let it through
+    gain = np.abs(oracle_logits(seen_cfg, W, seq)[0][-1] - without[-1]).max()
+    assert gain > 0.5, f"{name}: the planted key does not stand out ({gain})"
+    ref = oracle_logits(cfg, W, seq)[0]
+    n = make_engine(cfg, W, dtype, max_tokens=256, page_size=64 if name == "page_border" else 16)
+    got = run_cut(n, 0, seq, [n_tok - 40, 1] if decode else [n_tok])
+    e = row_err(got[-1:], ref[-1:])
+    assert e < TOL[dtype], f"{name} ({'decoded' if decode else 'prompt'}): {e:.3e}"
+    assert row_err(got, ref) < TOL[dtype]
+    n.close()
+
+
+def test_borrowed_keys_are_the_owner_layers_normed_keys():
+  """a layer that reads another layer's keys/values sees them as the owner's cache holds them (after the owner's key norm), under
+  its own mask: with a large key-norm weight on one channel of the owner a wrong source would show at once"""
+  cfg = config([attention(heads=2, kv_heads=2, dim=8, vdim=8, chunk=None), delta(heads=2, kv_heads=1, dim=8, vdim=8),
+                attention(heads=2, kv_heads=2, dim=8, vdim=8, chunk=6, kv_from=0)], width=32)
+  W = bo.random_weights(cfg, 5)
+  W["l0.mix.k.norm"][3] = 6.0
+  n = make_engine(cfg, W, "float32", page_size=4)
+  check(n, cfg, W, rand_tokens(cfg["vocab"], 45, 2), [19, 1], "float32")
+  n.close()
+
+
+# ---- several shards ----------------------------------------------------------------------------------------------------------
+def test_two_shards_hand_over_the_residual_stream():
+  cfg = config(MIXED)
+  W = bo.random_weights(cfg, 31)
+  a = make_engine(cfg, W, "float32", start=0, end=2)          # the borrowing layer 2 stays with its owner, layer 1
+  b = make_engine(cfg, W, "float32", start=3, end=4)
+  toks = rand_tokens(cfg["vocab"], 19, 7)
+  ref = oracle_logits(cfg, W, toks)[0]
+  hid = a.step([0], [toks[:12]])
+  lg, _ = b.step([0], [hid], want=list(range(12)))
+  assert row_err(lg, ref[:12]) < TOL["float32"]
+  hid = a.step([0], [toks[12:]])
+  lg, _ = b.step([0], [hid], want=list(range(7)))
+  assert row_err(lg, ref[12:]) < TOL["float32"]
+  a.close()
+  b.close()
+  with pytest.raises(Exception, match="earlier layer of this shard"):
+    make_engine(cfg, W, "float32", start=2, end=4)
+
+
+# ---- the loader and the entry points -----------------------------------------------------------------------------------------
+def write_model_dir(path, cfg, W):
+  hdr, blobs, at = {}, [], 0
+  for k, t in W.items():
+    raw = bf16_bits(t).tobytes()
+    hdr[k] = {"dtype": "BF16", "shape": list(t.shape), "data_offsets": [at, at + len(raw)]}
+    blobs.append(raw)
+    at += len(raw)
+  h = json.dumps(hdr).encode()
+  with open(path / "model.safetensors", "wb") as f:
+    f.write(struct.pack("<Q", len(h)) + h + b"".join(blobs))
+  with open(path / "config.json", "w") as f:
+    json.dump(cfg, f)
+
+
+def test_model_directory_loader_is_strict(tmp_path):
+  from xotorch_b200.models import load_model_config, make_native
+  cfg = config(MIXED)
+  W = bo.random_weights(cfg, 3)
+  write_model_dir(tmp_path, cfg, W)
+  n = make_native(load_model_config(tmp_path), 0, "float32")
+  n.load_dir(tmp_path)
+  n.begin_pool(64, 1, 8)
+  check(n, cfg, W, rand_tokens(cfg["vocab"], 12, 1), [12], "float32")
+  n.close()
+  for missing in ("l0.mix.q.conv", "l1.mlp.e3.up", "l2.mix.r2", "final.norm.b", "pos"):
+    bad = dict(W)
+    del bad[missing]
+    write_model_dir(tmp_path, cfg, bad)
+    with pytest.raises(Exception, match=missing.replace(".", r"\.")):
+      make_native(load_model_config(tmp_path), 0, "float32").load_dir(tmp_path)
+  bad = dict(W)
+  bad["l2.mix.k"] = torch.zeros(16, 48)                # the borrowing layer has no key tensors
+  write_model_dir(tmp_path, cfg, bad)
+  with pytest.raises(Exception, match=r"l2\.mix\.k"):
+    make_native(load_model_config(tmp_path), 0, "float32").load_dir(tmp_path)
+
+
+def oracle_greedy(cfg, W, prompt, n_new):
+  seq, ids, gaps = list(prompt), [], []
+  for _ in range(n_new):
+    lg = oracle_logits(cfg, W, np.array(seq))[0][-1]
+    top = np.sort(lg)[-2:]
+    ids.append(int(np.argmax(lg)))
+    gaps.append(float(top[1] - top[0]))
+    seq.append(ids[-1])
+  return ids, gaps
+
+
+@pytest.mark.parametrize("dtype,budget", [("float32", 2048), ("bfloat16", 7)])
+def test_greedy_generation_through_the_batch_scheduler(dtype, budget):
+  from xotorch_b200.scheduler import ContinuousBatch
+  cfg = config(MIXED)
+  W = bo.random_weights(cfg, 8)
+  n = make_engine(cfg, W, dtype)
+  events = []
+  sched = ContinuousBatch(n, max_requests=3, max_tokens=160, page_size=8, token_budget=budget,
+                          on_token=lambda rid, toks, fin: events.append((rid, list(toks), fin)))
+  reqs = [(f"r{i}", rand_tokens(cfg["vocab"], L, 70 + i), g) for i, (L, g) in enumerate([(5, 9), (17, 4), (1, 12), (26, 6), (3, 1)])]
+  for rid, p, g in reqs[:3]:
+    sched.submit(rid, p, g)
+  sched.step()
+  for rid, p, g in reqs[3:]:
+    sched.submit(rid, p, g)                           # joins while others are running
+  out = sched.run_until_idle()
+  for rid, p, g in reqs:
+    ids, gaps = oracle_greedy(cfg, W, p, g)
+    assert len(out[rid]) == g
+    if out[rid] != ids:                               # after a near tie the continuations differ legitimately
+      d = next(i for i in range(g) if out[rid][i] != ids[i])
+      assert gaps[d] < (1e-3 if dtype == "float32" else 0.15), f"{rid}: ids leave the oracle's at step {d} with a clear gap {gaps[d]}"
+    assert [e[1][0] for e in events if e[0] == rid] == out[rid]
+  st = n.cache_stats()
+  assert st["pages_free"] == st["pages_total"], "finished requests must give their pages back"
+  n.close()
+
+
+def test_command_line_generates_from_a_model_directory(tmp_path, capsys):
+  from xotorch_b200.cli import main
+  cfg = config(MIXED)
+  W = bo.random_weights(cfg, 8)
+  write_model_dir(tmp_path, cfg, W)
+  prompts = [rand_tokens(cfg["vocab"], 6, 1), rand_tokens(cfg["vocab"], 11, 2)]
+  arg = ";".join(",".join(str(int(t)) for t in p) for p in prompts)
+  assert main(["generate", "--model", str(tmp_path), "--prompt-ids", arg, "--max-tokens", "5", "--dtype", "float32"]) == 0
+  lines = [json.loads(l) for l in capsys.readouterr().out.strip().splitlines()]
+  for p, line in zip(prompts, lines):
+    ids, gaps = oracle_greedy(cfg, W, p, 5)
+    if line["ids"] != ids:
+      d = next(i for i in range(5) if line["ids"][i] != ids[i])
+      assert gaps[d] < 1e-3
+
+
+def test_trace_replay_of_a_model_directory(tmp_path):
+  """the token-trace replayer on a model directory: prompts in one batch, then decoding together, one request ending early"""
+  from xotorch_b200.trace_replay import TraceReplayer
+  cfg = config(MIXED)
+  W = bo.random_weights(cfg, 15)
+  model, out = tmp_path / "m", tmp_path / "o"
+  model.mkdir()
+  write_model_dir(model, cfg, W)
+  a, b = rand_tokens(cfg["vocab"], 22, 1), rand_tokens(cfg["vocab"], 9, 2)
+  ra, rb = oracle_logits(cfg, W, a)[0], oracle_logits(cfg, W, b)[0]
+  rp = TraceReplayer(model, "float32", out, max_tokens=64)
+  rp.run_step({"step": 0, "entries": [{"id": "a", "tokens": a[:18].tolist(), "want": [0, 17]}, {"id": "b", "tokens": b[:8].tolist(), "want": [7]}], "end": []})
+  rp.run_step({"step": 1, "entries": [{"id": "a", "tokens": [int(a[18])], "want": [0]}, {"id": "b", "tokens": [int(b[8])], "want": [0]}], "end": ["b"]})
+  rp.run_step({"step": 2, "entries": [{"id": "a", "tokens": a[19:22].tolist(), "want": []}], "end": ["a"]})
+  V = cfg["vocab"]
+  s0 = np.fromfile(out / "0.f32", dtype="<f4").reshape(-1, V)
+  s1 = np.fromfile(out / "1.f32", dtype="<f4").reshape(-1, V)
+  assert row_err(s0, np.stack([ra[0], ra[17], rb[7]])) < TOL["float32"]
+  assert row_err(s1, np.stack([ra[18], rb[8]])) < TOL["float32"]
+  assert not (out / "2.f32").exists()
+  rp.close()
+
+
+# ---- decode steps replayed from CUDA graphs ----------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_graph_replay_of_decode_steps_changes_nothing(dtype):
+  cfg = config(MIXED)
+  W = bo.random_weights(cfg, 19)
+  seqs = [rand_tokens(cfg["vocab"], 300, 40 + i) for i in range(3)]
+  starts = [240, 3, 17]
+
+  def run(graphs):
+    n = make_engine(cfg, W, dtype, max_tokens=1000, max_requests=3, page_size=8)
+    n.set_graphs(graphs)
+    n.step([0, 1, 2], [s[:k] for s, k in zip(seqs, starts)])
+    out, live = [], [0, 1, 2]
+    for t in range(40):
+      if t == 25:
+        live = [0, 2]
+        n.clear_request(1)
+      lg, _ = n.step(live, [seqs[i][starts[i] + t:starts[i] + t + 1] for i in live])
+      out.append(lg)
+    replays = n.graph_replays()
+    n.close()
+    return out, replays
+
+  plain, r0 = run(False)
+  replayed, r1 = run(True)
+  assert r0 == 0 and r1 >= 30
+  for a, b in zip(plain, replayed):
+    assert np.array_equal(a, b)
+  ref = oracle_logits(cfg, W, seqs[0][:280])[0]
+  got = np.stack([x[0] for x in replayed])
+  assert row_err(got, ref[240:280]) < TOL[dtype]
+
+
+# ---- sizes the tensor-core paths take ----------------------------------------------------------------------------------------
+def test_prompt_kernels_on_aligned_sizes_equal_the_plain_ones():
+  """sizes that are multiples of 8 and prompts of hundreds of rows: the bf16 engine runs its products (and whatever else it has a
+  tensor-core form of) there; the results must agree with the fp32-FMA tiles on the same 16-bit operands and with the oracle"""
+  layers = [delta(heads=4, kv_heads=2, dim=16, vdim=24, conv=4, mlp=moe(8, 2, (4, 2), 32)),
+            attention(heads=4, kv_heads=2, dim=16, vdim=24, chunk=96, mlp=dense(72)),
+            attention(heads=4, kv_heads=2, dim=16, vdim=24, chunk=40, kv_from=1, mlp=moe(4, 2, None, 40)),
+            attention(heads=2, kv_heads=2, dim=32, vdim=64, chunk=None, mlp=dense(200))]
+  cfg = config(layers, width=64, vocab=136, max_positions=700)
+  W = bo.random_weights(cfg, 12)
+  n = make_engine(cfg, W, "bfloat16", max_tokens=1400, max_requests=3, page_size=32)
+  a, b = rand_tokens(cfg["vocab"], 300, 9), rand_tokens(cfg["vocab"], 150, 10)
+  ra, rb = oracle_logits(cfg, W, a)[0], oracle_logits(cfg, W, b)[0]
+  before = n.tensor_core_launches()
+  lg1, _ = n.step([0, 1], [a[:200], b], want=list(range(350)))          # a's first 200 rows and all of b in one batch
+  lg2, _ = n.step([0], [a[200:]], want=list(range(100)))               # the rest of a starts inside a block
+  assert n.tensor_core_launches() > before
+  tc_a = np.concatenate([lg1[:200], lg2])
+  assert row_err(tc_a, ra) < TOL["bfloat16"] and row_err(lg1[200:], rb) < TOL["bfloat16"]
+  n.set_gemm_mode(1)
+  n.set_attention_mode(1)
+  fma = run_cut(n, 2, a, [200, 100])
+  assert row_err(fma, ra) < TOL["bfloat16"]
+  assert row_err(tc_a, fma.astype(np.float64)) < 0.03, "same operands, fp32 accumulation in both"
+  n.close()

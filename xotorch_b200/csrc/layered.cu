@@ -398,8 +398,8 @@ static int upload_tensor(xotb200_lm* e, Dest& d, const void* host_bf16) {
 
 // does a tensor name belong to this shard? (so that an unknown name there is an error, and anything else is skipped)
 static bool owned_name(const xotb200_lm* e, const std::string& name) {
-  if (name == "embed") return e->first;
-  if (name == "head" || name == "final.norm") return e->last;
+  if (name == "embed" || name == "pos") return e->first;
+  if (name == "head" || name == "final.norm" || name == "final.norm.b") return e->last;
   if (name.size() > 1 && name[0] == 'l' && isdigit((unsigned char)name[1])) {
     const int li = atoi(name.c_str() + 1);
     return li >= e->cfg.start_layer && li <= e->cfg.end_layer;
@@ -785,7 +785,7 @@ static int gqa_key_runs(const xotb200_lm* e, const xotb200_lm_layer& s, int n_it
   const int rep = s.heads / s.kv_heads, qpi = gqa_rows_per_item(s), pairs = qpi * rep, nw = std::min(32, pairs), ytiles = cdiv(pairs, nw);
   int span = std::max(1, max_len);
   if (s.window > 0) span = std::min(span, s.window + qpi);
-  if (s.chunk > 0) span = std::min(span, s.chunk);
+  if (s.chunk > 0) span = std::min(span, s.chunk + qpi - 1);   // an item's rows may straddle two blocks: its keys start at the first row's block
   int splits = 1;
   const long ctas = (long)n_items * s.kv_heads * ytiles;
   if (ctas > 0 && ctas < e->sm_count) splits = std::max(1, std::min(std::min(32, cdiv(span, 32)), cdiv(2 * e->sm_count, ctas)));
