@@ -2,6 +2,10 @@
 few sizes that resemble a real model's layers, beside the shard engine's Llama decoder of the same width, depth and (to a few
 per cent) weight bytes.  One JSON line per size; nothing here touches bench.py's default workload.
 
+`--layered-family bufulorn`: the same for Bufulorn-shaped models (gated delta rule, grouped-query attention with shared keys /
+values, dense and mixture-of-experts feed-forwards) beside the closest existing family on the same engine, a Zokuvik model of
+the same width and depth whose feed-forward size is chosen so that the weight bytes match.
+
 Timing: every number is the device time of the step(s) (CUDA events on the engine's stream, `last_step_ms` / the ring's own
 timer), after warm-up; the weights of every size are larger than L2 from `medium` on, and each prompt step streams all of them.
 Roofline denominators come from MEASURED_PEAKS.json (fallback: the profiling recipe's numbers)."""
@@ -42,6 +46,36 @@ def zokuvik_config(s: dict):
   return cfg, shapes
 
 
+# Bufulorn shapes at the same widths: value heads x size of the delta layers as above, half as many query/key heads; attention
+# with 4 query heads per key/value head; 16 experts of a quarter of the dense inner size, 4 per token (as many active weights as
+# the dense layers), in 4 groups of which 2 are kept; blocks of 1024 positions
+BUFULORN = {
+  "small": dict(heads=16, kv_heads=4, dim=64, vdim=64, dheads=16, dkv=8, ddim=64, dvdim=64),
+  "medium": dict(heads=16, kv_heads=4, dim=128, vdim=128, dheads=32, dkv=16, ddim=64, dvdim=64),
+  "large": dict(heads=32, kv_heads=8, dim=128, vdim=128, dheads=32, dkv=16, ddim=128, dvdim=128),
+}
+EXPERTS, TOP, GROUPS, KEEP, TAPS = 16, 4, 4, 2, 4
+
+
+def bufulorn_config(s: dict, b: dict, context: int):
+  def att(src, mlp):
+    m = {"heads": b["heads"], "kv_heads": b["kv_heads"], "dim": b["dim"], "vdim": b["vdim"], "scale": float(b["dim"] ** -0.5), "softcap": 50.0,
+         "mask": {"size": WINDOW}}
+    if src is not None:
+      m["kv_from"] = src
+    return {"type": "attention", "mixer": m, "mlp": mlp}
+  dense = {"kind": "dense", "ff": s["ff"]}
+  moe = {"kind": "moe", "router": {"experts": EXPERTS, "top": TOP, "groups": {"count": GROUPS, "keep": KEEP}}, "expert": {"ff": s["ff"] // 4}}
+  layers = []
+  for r in range(s["repeats"]):
+    layers += [{"type": "delta", "mixer": {"heads": b["dheads"], "kv_heads": b["dkv"], "dim": b["ddim"], "vdim": b["dvdim"], "conv": TAPS}, "mlp": dense},
+               att(None, moe), att(3 * r + 1, dense)]
+  cfg = {"architecture": "Bufulorn", "width": s["width"], "vocab": s["vocab"], "max_positions": context, "norm": {"eps": 1e-5}, "layers": layers}
+  n_moe = sum(1 for l in layers if l["mlp"]["kind"] == "moe")
+  idle = n_moe * (EXPERTS - TOP) * 3 * (s["ff"] // 4) * s["width"] * 2          # bytes of the experts one token does not use
+  return cfg, idle
+
+
 def peaks():
   p = ROOT / "MEASURED_PEAKS.json"
   if p.exists():
@@ -53,14 +87,17 @@ def peaks():
   return 6650.0, 1590.0, "fallback"
 
 
-def layered_numbers(s: dict, prompts, decode_ctx: int, decode_batches, steps: int, warmup: int) -> dict:
+def layered_numbers(s: dict, prompts, decode_ctx: int, decode_batches, steps: int, warmup: int, cfg=None, shapes=None, idle_bytes: int = 0) -> dict:
+  """idle_bytes: weights a token does not touch (experts it is not routed to); the FLOP and byte figures count the others"""
   from .layered import LayeredShard
-  cfg, shapes = zokuvik_config(s)
+  if cfg is None:
+    cfg, shapes = zokuvik_config(s)
   eng = LayeredShard(cfg, 0, "bfloat16")
-  eng.set_shard(0, len(cfg["layers"]) - 1, shapes)
+  eng.set_shard(0, len(cfg["layers"]) - 1, shapes or {})
   eng.init_synthetic(7)
   wbytes = eng.weight_bytes()
-  body = wbytes - 2 * s["vocab"] * s["width"]                       # a prompt step streams the body once + one row of the embedding per token
+  # a prompt step streams the body once + one row of the embedding (and of the position table) per token
+  body = wbytes - 2 * s["vocab"] * s["width"] - int(cfg.get("max_positions", 0)) * s["width"] * 2 - idle_bytes
   rng = np.random.default_rng(0)
   out = {"weight_bytes": wbytes, "prefill": {}, "decode": {}}
   max_b = max(decode_batches)
@@ -147,10 +184,46 @@ def llama_numbers(s: dict, target_bytes: int, prompts, decode_ctx: int, steps: i
   return out
 
 
+def zokuvik_of_bytes(s: dict, target: int) -> dict:
+  """the Zokuvik shape of this width and depth whose feed-forward size makes its weight bytes `target`"""
+  from .layered import LayeredShard
+  def nbytes(ff):
+    cfg, shapes = zokuvik_config(dict(s, ff=ff))
+    eng = LayeredShard(cfg, 0, "bfloat16")
+    eng.set_shard(0, len(cfg["layers"]) - 1, shapes)
+    n = eng.weight_bytes()
+    eng.close()
+    return n
+  b0, b1 = nbytes(1024), nbytes(2048)
+  ff = int(max(256, 1024 + (target - b0) / ((b1 - b0) / 1024)) // 64 * 64)
+  return dict(s, ff=ff)
+
+
+def run_bufulorn(args, sizes, prompts, hbm, tf, src) -> None:
+  for name in sizes:
+    s, b = SIZES[name], BUFULORN[name]
+    warm = max(3, args.warmup)
+    context = max(max(prompts), 1024 + 9 * (args.steps * 8 + warm)) + 64
+    cfg, idle = bufulorn_config(s, b, context)
+    bu = layered_numbers(s, prompts, decode_ctx=1024, decode_batches=[1, 8], steps=args.steps, warmup=warm, cfg=cfg, idle_bytes=idle)
+    zs = zokuvik_of_bytes(s, bu["weight_bytes"])
+    z = layered_numbers(zs, prompts, decode_ctx=1024, decode_batches=[1, 8], steps=args.steps, warmup=warm)
+    line = {"bench": "layered", "family": "bufulorn", "size": name, "dtype": "bf16", "data": "synthetic", "shape": dict(s, **b), "bufulorn": bu,
+            "idle_expert_bytes": idle, "zokuvik_same_size": z, "zokuvik_ff": zs["ff"], "peaks": {"hbm_gbs": hbm, "bf16_tflops": tf, "source": src},
+            "frac_of_peak": {
+              "bufulorn_decode1_hbm": round(bu["decode"]["1"]["gbs_weights_device"] / hbm, 3),
+              "zokuvik_decode1_hbm": round(z["decode"]["1"]["gbs_weights_device"] / hbm, 3),
+              **{f"bufulorn_prefill{n}_tensor": round(bu["prefill"][str(n)]["tflops_weights"] / tf, 3) for n in prompts},
+              **{f"zokuvik_prefill{n}_tensor": round(z["prefill"][str(n)]["tflops_weights"] / tf, 3) for n in prompts}}}
+    print(json.dumps(line), flush=True)
+
+
 def run(args) -> None:
   hbm, tf, src = peaks()
   sizes = [x for x in (args.layered_sizes or "small,medium,large").split(",") if x]
   prompts = [int(x) for x in (args.layered_prompts or "1024,4096").split(",")]
+  if (getattr(args, "layered_family", "") or "zokuvik") == "bufulorn":
+    return run_bufulorn(args, sizes, prompts, hbm, tf, src)
   for name in sizes:
     s = SIZES[name]
     z = layered_numbers(s, prompts, decode_ctx=1024, decode_batches=[1, 8], steps=args.steps, warmup=max(3, args.warmup))

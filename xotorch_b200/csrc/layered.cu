@@ -73,6 +73,7 @@ struct Dest {
   bool has2 = false;  // a second, untransposed copy at elem_off2 (W_uk: the expanded prompt attention reads it row-major)
   size_t elem_off2 = 0;
   int tr_heads = 0;   // > 0: the file's [heads * d, cols] matrix is stored head by head TRANSPOSED, [heads][cols][d]
+  int il8 = -1;       // 0 / 1: row r goes to row (r / 8) * 16 + il8 * 8 + r % 8 of the matrix at elem_off (gate / up rows of an expert)
 };
 
 struct LmLayer {
@@ -134,7 +135,11 @@ struct xotb200_lm {
   float *x = nullptr, *y = nullptr, *proj = nullptr, *qraw = nullptr, *qfull = nullptr, *wlog = nullptr, *oraw = nullptr, *du = nullptr, *dau = nullptr, *logits = nullptr;
   float *dkk = nullptr, *drr = nullptr, *cvb = nullptr, *moe_wts = nullptr;   // gated delta rule: write keys, read-out vectors, filtered channels; expert weights
   int* moe_ids = nullptr;
-  void* mact = nullptr;                                // experts' inner activations [rows, top, F] of T
+  void* mact = nullptr;                                // experts' inner activations [rows, top, F] of T (grouped form: [padded pairs, F])
+  void* moe_xg = nullptr;                              // grouped form: the rows sorted by expert [padded pairs, D] (bf16)
+  float* moe_yg = nullptr;                             // grouped form: the experts' outputs [padded pairs, D]
+  int* moe_plan = nullptr;                             // counts[E], starts[E + 1], cursor[E], place[rows * top], tile_expert[tiles]
+  int moe_tiles_cap = 0;
   int max_conv = 0, max_top = 0, max_eff = 0, max_experts = 0;
   size_t final_norm_b = 0, pos_table = 0;
   void *h = nullptr, *cqn = nullptr, *qn = nullptr, *olat = nullptr, *oh = nullptr, *act = nullptr, *th = nullptr, *hw = nullptr;
@@ -155,6 +160,7 @@ struct xotb200_lm {
   std::map<std::array<long, 5>, GraphSlot> graphs;
   int64_t graph_replays = 0;
   bool flash_fits = true;                              // every attention layer fits the expanded kernel's tile sizes
+  bool gqa_flash_fits = true;                          // every key/value-cache attention layer fits the tensor-core prompt kernel (16-byte rows)
   bool flash_on = true;                                // bf16: prompt portions of FLASH_MIN_ROWS rows or more use the expanded tensor-core attention
   std::vector<int> stage_build;
   int64_t launches = 0, tc_launches = 0, flash_launches = 0;
@@ -290,6 +296,7 @@ static int build_layout(xotb200_lm* e, const xotb200_lm_layer* all) {
       e->max_q = std::max(e->max_q, H * dk);
       e->max_qfull = std::max(e->max_qfull, H * dk);
       e->max_oh = std::max(e->max_oh, H * dv);
+      if (dk % 8 || dv % 8 || dk > 256 || dv > 128) e->gqa_flash_fits = false;
     } else if (s.mixer == XOTB200_LM_MIX_GATED_DELTA) {
       const int H = s.heads, G = s.kv_heads, dk = s.dim, dv = s.vdim, C = 2 * G * dk + H * dv;
       REQUIRE(G >= 1 && H % G == 0, "layer %d: %d value heads do not divide into %d query/key heads", li, H, G);
@@ -342,7 +349,8 @@ static int build_layout(xotb200_lm* e, const xotb200_lm_layer* all) {
       for (int x = 0; x < E; ++x) {
         const std::string ep = p + "mlp.e" + std::to_string(x) + ".";
         dest(ep + "gate", L.w_gu, F, D, x * 2 * F);
-        dest(ep + "up", L.w_gu, F, D, x * 2 * F + F);
+        dest(ep + "up", L.w_gu, F, D, x * 2 * F + (F % 8 ? F : 0));
+        if (F % 8 == 0) { e->dests[ep + "gate"].il8 = 0; e->dests[ep + "up"].il8 = 1; }   // gate and up rows interleaved in eights
         dest(ep + "down", L.w_edown, D, F, x * D);
       }
       e->max_top = std::max(e->max_top, s.top);
@@ -378,6 +386,9 @@ static int upload_tensor(xotb200_lm* e, Dest& d, const void* host_bf16) {
       const int dh = d.rows / d.tr_heads;
       if (e->esz == 2) store_heads_transposed_kernel<bf16><<<grid, 256, 0, e->stream>>>(tmp, at<bf16>(e, off), d.tr_heads, dh, d.cols);
       else store_heads_transposed_kernel<float><<<grid, 256, 0, e->stream>>>(tmp, at<float>(e, off), d.tr_heads, dh, d.cols);
+    } else if (d.il8 >= 0) {
+      if (e->esz == 2) store_rows_interleaved8_kernel<bf16><<<grid, 256, 0, e->stream>>>(tmp, at<bf16>(e, off), d.rows, d.cols, d.il8);
+      else store_rows_interleaved8_kernel<float><<<grid, 256, 0, e->stream>>>(tmp, at<float>(e, off), d.rows, d.cols, d.il8);
     } else if (e->esz == 2) store_rows_kernel<bf16><<<grid, 256, 0, e->stream>>>(tmp, at<bf16>(e, off), n);
     else store_rows_kernel<float><<<grid, 256, 0, e->stream>>>(tmp, at<float>(e, off), n);
     if (d.has2) {
@@ -466,7 +477,7 @@ static int product_tc(xotb200_lm* e, const bf16* A, long lda, long a_batch, cons
   const int nt = (N > 64 && M > LTC_M) ? 128 : 64;   // one row tile: narrower column tiles, twice the CTAs streaming weights
   CUtensorMap ma, mb;
   if (!make_map3(&ma, A, M, K, lda, a_batch, batch, LTC_M) || !make_map3(&mb, B, N, K, ldb, b_batch, batch, nt)) return 0;
-  LtcArgs a{M, N, K, C, ldc, c_batch, e->d_err, static_cast<const bf16*>(epi)};
+  LtcArgs a{M, N, K, C, ldc, c_batch, e->d_err, static_cast<const bf16*>(epi), nullptr};
   if (nt == 128) TRY((launch_ltc<128, EPI, TC>(e, ma, mb, a, batch)));
   else TRY((launch_ltc<64, EPI, TC>(e, ma, mb, a, batch)));
   return 1;
@@ -550,7 +561,17 @@ static int ensure_scratch(xotb200_lm* e, int M, int n_want) {
     if (e->max_top) {
       TRY(regrow(e->moe_ids, m * e->max_top * 4));
       TRY(regrow(e->moe_wts, m * e->max_top * 4));
-      TRY(regrow(e->mact, m * e->max_top * e->max_eff * z));
+      // the grouped form pads every expert's run to whole 128-row tiles
+      const size_t tiles = (m * e->max_top + LTC_M - 1) / LTC_M + e->max_experts, pairs_pad = tiles * LTC_M;
+      TRY(regrow(e->mact, pairs_pad * e->max_eff * z));
+      if (z == 2) {
+        TRY(regrow(e->moe_xg, pairs_pad * D * 2));
+        TRY(regrow(e->moe_yg, pairs_pad * D * 4));
+        const size_t ints = 3 * (size_t)e->max_experts + 1 + m * e->max_top + tiles;
+        TRY(regrow(e->moe_plan, ints * 4));
+        CK(cudaMemsetAsync(e->moe_plan, 0, ints * 4, e->stream));
+        e->moe_tiles_cap = (int)tiles;
+      }
     }
     TRY(regrow(e->h, m * D * z));
     TRY(regrow(e->cqn, m * e->max_qr * z));
@@ -604,6 +625,8 @@ struct StepPlan {
   std::map<int, Flash> flash;
   int max_len = 0;                                     // longest request after this step (bounds every key range)
   int max_rows = 0;                                    // most rows one request brings
+  const GqaTile* gqa_tiles = nullptr;                  // key/value-cache attention, long portions (bf16): 64-row tiles
+  int n_gqa_tiles = 0;
   bool any_short = true;                               // some request goes through the absorbed kernel
 };
 
@@ -805,7 +828,8 @@ static int gqa_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
   const int slots = H + (own ? 2 * G : 0);
   gqa_prepare_kernel<T><<<cdiv((long)M * slots, 8), 256, 0, e->stream>>>(
       e->proj, L.n_in, L.c_q, L.c_kk, L.c_vv, s.proj_bias ? at<T>(e, L.b_in) : nullptr, s.qk_norm ? at<T>(e, L.q_norm) : nullptr,
-      s.qk_norm && own ? at<T>(e, L.k_norm) : nullptr, e->cfg.norm_eps, H, G, dk, dv, own ? 1 : 0, sp.row_slot, sp.row_pos, pg, pool, e->qfull, nullptr, M);
+      s.qk_norm && own ? at<T>(e, L.k_norm) : nullptr, e->cfg.norm_eps, H, G, dk, dv, own ? 1 : 0, sp.row_slot, sp.row_pos, pg, pool, e->qfull,
+      sp.n_gqa_tiles > 0 ? static_cast<bf16*>(e->q16) : nullptr, M);
   CK(cudaGetLastError());
   e->launches++;
   const GqaScore sc{s.scale, s.softcap, s.window, s.chunk, s.dist_bias ? at<T>(e, L.r1) : nullptr, s.dist_bias ? at<T>(e, L.r2) : nullptr};
@@ -838,6 +862,27 @@ static int gqa_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
                                                                                      static_cast<T*>(e->oh));
       CK(cudaGetLastError());
       e->launches++;
+    }
+  }
+  if constexpr (std::is_same<T, bf16>::value) {
+    if (sp.n_gqa_tiles > 0) {
+      // long portions: streaming softmax on the tensor cores, keys and values straight from the pages
+      const int dqp = (dk + 15) & ~15, dvt = dv <= 64 ? 8 : 16;
+      const size_t fsm = ((size_t)3 * 64 * (dqp + 8) + (size_t)2 * 64 * (8 * dvt + 8)) * 2;
+      const dim3 grid(sp.n_gqa_tiles, H);
+#define LAUNCH_GQA_FLASH(DVT)                                                                                                              \
+  do {                                                                                                                                     \
+    auto kern = gqa_flash_kernel<DVT>;                                                                                                     \
+    TRY(opt_in_smem(kern, fsm));                                                                                                           \
+    kern<<<grid, 128, fsm, e->stream>>>(static_cast<const bf16*>(e->q16), pool, pg, sp.gqa_tiles, H, G, dk, dv, sc, gate, s.out_gate, L.n_in, \
+                                        L.c_g, static_cast<bf16*>(e->oh));                                                                  \
+  } while (0)
+      if (dvt == 8) LAUNCH_GQA_FLASH(8);
+      else LAUNCH_GQA_FLASH(16);
+#undef LAUNCH_GQA_FLASH
+      CK(cudaGetLastError());
+      e->launches++;
+      e->flash_launches++;
     }
   }
   TRY((product<T, T, float, 0>(e, static_cast<T*>(e->oh), (long)H * dv, 0, at<T>(e, L.wo), (long)H * dv, 1, 0, e->y, D, 0, M, D, H * dv, 1)));
@@ -874,6 +919,23 @@ static int gated_delta_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
   return 0;
 }
 
+// Rows sorted by expert, every run padded to whole row tiles: C[p, :] = A[p, :] B[tile_batch[p / 128]]^T on the tensor cores.
+// 1 = launched, 0 = the operands cannot be described to TMA
+template <int EPI, typename TC>
+static int grouped_product(xotb200_lm* e, const bf16* A, long lda, const bf16* B, long ldb, long b_batch, int n_batch, TC* C, long ldc, int m_pad, int N,
+                           int K, const int* tile_batch) {
+  const int nt = N > 64 ? 128 : 64;
+  CUtensorMap ma, mb;
+  if (!make_map3(&ma, A, m_pad, K, lda, 0, 1, LTC_M) || !make_map3(&mb, B, N, K, ldb, b_batch, n_batch, nt)) return 0;
+  LtcArgs a{m_pad, N, K, C, ldc, 0, e->d_err, nullptr, tile_batch};
+  if (nt == 128) TRY((launch_ltc<128, EPI, TC>(e, ma, mb, a, 1)));
+  else TRY((launch_ltc<64, EPI, TC>(e, ma, mb, a, 1)));
+  return 1;
+}
+
+// rows from which the experts run as grouped tensor-core products (below: every (row, expert) pair streams its expert)
+static const int MOE_GROUPED_MIN_ROWS = 17;
+
 static bool layer_has_ff(const xotb200_lm_layer& s) { return s.ff_kind == XOTB200_LM_FF_MOE ? s.experts > 0 : s.ff > 0; }
 
 // the feed-forward of a layer: h (T) -> y (fp32)
@@ -887,10 +949,35 @@ static int feed_forward(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
     moe_router_kernel<T><<<cdiv(M, 4), 128, (size_t)4 * (E + 32) * 4, e->stream>>>(h, D, at<T>(e, L.router), E, s.groups, s.groups_keep, top, e->moe_ids, e->moe_wts, M);
     CK(cudaGetLastError());
     e->launches++;
+    const int il8 = F % 8 == 0 ? 1 : 0;
+    if constexpr (std::is_same<T, bf16>::value) {
+      if (M >= MOE_GROUPED_MIN_ROWS && e->gemm_mode != 1 && il8 && D % 8 == 0) {
+        const int pairs = M * top, tiles = cdiv(pairs, LTC_M) + E, m_pad = tiles * LTC_M;
+        REQUIRE(tiles <= e->moe_tiles_cap, "internal: the expert tile list was not sized for this step");
+        int *counts = e->moe_plan, *starts = counts + e->max_experts, *cursor = starts + e->max_experts + 1, *place = cursor + e->max_experts,
+            *tile_expert = place + (size_t)e->m_cap * e->max_top;
+        bf16* xg = static_cast<bf16*>(e->moe_xg);
+        moe_count_kernel<<<cdiv(pairs, 256), 256, 0, e->stream>>>(e->moe_ids, pairs, counts);
+        moe_plan_kernel<<<1, 256, 0, e->stream>>>(counts, E, LTC_M, tiles, starts, cursor, tile_expert);
+        moe_scatter_kernel<bf16><<<cdiv(pairs, 8), 256, 0, e->stream>>>(h, D, e->moe_ids, pairs, top, starts, cursor, place, xg);
+        CK(cudaGetLastError());
+        e->launches += 3;
+        int r = grouped_product<3, bf16>(e, xg, D, at<bf16>(e, L.w_gu), D, (long)2 * F * D, E, static_cast<bf16*>(e->mact), F, m_pad, 2 * F, D, tile_expert);
+        if (r < 0) return r;
+        if (r == 1) r = grouped_product<0, float>(e, static_cast<bf16*>(e->mact), F, at<bf16>(e, L.w_edown), F, (long)D * F, E, e->moe_yg, D, m_pad, D, F, tile_expert);
+        if (r < 0) return r;
+        if (r == 1) {
+          moe_combine_kernel<<<M, 256, 0, e->stream>>>(e->moe_yg, place, e->moe_wts, top, D, e->y);
+          CK(cudaGetLastError());
+          e->launches++;
+          return 0;
+        }
+      }
+    }
     {
       auto kern = moe_rows_up_kernel<T>;
       TRY(opt_in_smem(kern, (size_t)D * 4));
-      kern<<<dim3(M, top, std::max(1, std::min(cdiv(F, 8), 64))), 256, (size_t)D * 4, e->stream>>>(h, D, at<T>(e, L.w_gu), F, e->moe_ids, top, static_cast<T*>(e->mact));
+      kern<<<dim3(M, top, std::max(1, std::min(cdiv(F, 8), 64))), 256, (size_t)D * 4, e->stream>>>(h, D, at<T>(e, L.w_gu), F, il8, e->moe_ids, top, static_cast<T*>(e->mact));
       CK(cudaGetLastError());
       e->launches++;
     }
@@ -1110,7 +1197,7 @@ int xotb200_lm_destroy(xotb200_lm* e) {
   free_state(e);
   for (auto& L : e->layers)
     if (L.freqs) cudaFree(L.freqs);
-  void* ptrs[] = {e->dkk, e->drr, e->cvb, e->moe_ids, e->moe_wts, e->mact, e->du, e->dau, e->part, e->q16, e->cbuf, e->knx, e->vxx, e->blob, e->d_stage, e->x, e->y, e->proj, e->qraw, e->qfull, e->wlog, e->oraw, e->logits, e->h, e->cqn, e->qn, e->olat, e->oh, e->act,
+  void* ptrs[] = {e->moe_xg, e->moe_yg, e->moe_plan, e->dkk, e->drr, e->cvb, e->moe_ids, e->moe_wts, e->mact, e->du, e->dau, e->part, e->q16, e->cbuf, e->knx, e->vxx, e->blob, e->d_stage, e->x, e->y, e->proj, e->qraw, e->qfull, e->wlog, e->oraw, e->logits, e->h, e->cqn, e->qn, e->olat, e->oh, e->act,
                   e->th, e->hw, e->d_argmax, e->trace_buf};
   for (void* p : ptrs)
     if (p) cudaFree(p);
@@ -1151,7 +1238,7 @@ int xotb200_lm_init_synthetic(xotb200_lm* e, uint64_t seed) {
   for (auto& kv : e->dests) {
     Dest& d = kv.second;
     const std::string& name = kv.first;
-    const size_t n = (size_t)d.rows * d.cols, off = d.elem_off + (size_t)d.row_off * d.cols;
+    const size_t n = (size_t)d.rows * d.cols, off = d.elem_off + (size_t)d.row_off * d.cols + (d.il8 == 1 ? n : 0);   // interleaved pairs: any split will do
     float mean = 0.f, dev = 1.0f / sqrtf((float)d.cols);
     const auto ends = [&](const char* suf) { const size_t n = strlen(suf); return name.size() >= n && name.compare(name.size() - n, n, suf) == 0; };
     if (ends(".r1")) { mean = 0.1f; dev = 0.03f; }              // distance penalties stay positive
@@ -1382,7 +1469,8 @@ int xotb200_lm_step(xotb200_lm* e, int n_seq, const int32_t* slots, const int32_
   auto is_long = [&](int i) { return use_flash && counts[i] >= FLASH_MIN_ROWS; };
   std::map<int, std::pair<size_t, int>> item_off;
   sp.any_short = false;
-  auto is_long_gqa = [&](int) { return false; };
+  const bool use_gqa_flash = e->esz == 2 && e->flash_on && e->gqa_flash_fits;
+  auto is_long_gqa = [&](int i) { return use_gqa_flash && counts[i] >= FLASH_MIN_ROWS; };
   for (int qk : qpis) {
     std::vector<Item> it;
     const int q = qk < 0 ? -qk : qk;
@@ -1391,6 +1479,16 @@ int xotb200_lm_step(xotb200_lm* e, int n_seq, const int32_t* slots, const int32_
         for (int t = 0; t < counts[i]; t += q) it.push_back(Item{seqs[i].row0 + t, std::min(q, counts[i] - t), seqs[i].slot, seqs[i].pos0 + t});
     item_off[qk] = {push(it.data(), 4 * it.size()), (int)it.size()};
     if (!it.empty() && qk > 0) sp.any_short = true;
+  }
+  size_t gqa_tiles_off = 0;
+  int n_gqa_tiles = 0;
+  if (use_gqa_flash && std::any_of(qpis.begin(), qpis.end(), [](int q) { return q < 0; })) {
+    std::vector<GqaTile> gt;
+    for (int i = 0; i < n_seq; ++i)
+      if (is_long_gqa(i))
+        for (int t = 0; t < counts[i]; t += 64) gt.push_back(GqaTile{seqs[i].row0 + t, std::min(64, counts[i] - t), seqs[i].pos0 + t, seqs[i].slot});
+    gqa_tiles_off = push(gt.data(), 4 * gt.size());
+    n_gqa_tiles = (int)gt.size();
   }
   struct FlashOff { size_t reqs, tiles; int n_reqs, n_tiles, n_keys, max_keys; };
   std::map<int, FlashOff> flash_off;
@@ -1472,6 +1570,8 @@ int xotb200_lm_step(xotb200_lm* e, int n_seq, const int32_t* slots, const int32_
       sp.want = e->d_stage + 3 * M;
       sp.seqs = reinterpret_cast<const Item*>(e->d_stage + off_seqs);
       for (auto& kv : item_off) sp.items[kv.first] = {reinterpret_cast<const Item*>(e->d_stage + kv.second.first), kv.second.second};
+      sp.gqa_tiles = reinterpret_cast<const GqaTile*>(e->d_stage + gqa_tiles_off);
+      sp.n_gqa_tiles = n_gqa_tiles;
       for (auto& kv : flash_off) {
         StepPlan::Flash f;
         f.reqs = reinterpret_cast<const GatherReq*>(e->d_stage + kv.second.reqs);

@@ -207,50 +207,143 @@ __global__ void moe_router_kernel(const T* __restrict__ h, int D, const T* __res
 }
 
 // ---------------------------------------------------------------------------------------------------------------------------
+// Mixture of experts: layout of an expert's gate and up matrices.  w_gu is [E][2 F, D]; with il8 (F a multiple of 8) gate row f
+// and up row f sit at rows (f / 8) * 16 + f % 8 and (f / 8) * 16 + 8 + f % 8, so that a 16-column fragment of a product's output
+// holds 8 gate values next to their 8 up values and silu(gate) * up is formed in the epilogue; else gate rows come first, then up.
+// ---------------------------------------------------------------------------------------------------------------------------
+__device__ __host__ __forceinline__ size_t moe_gate_row(int f, int F, int il8) { return il8 ? (size_t)(f / 8) * 16 + f % 8 : (size_t)f; }
+__device__ __host__ __forceinline__ size_t moe_up_row(int f, int F, int il8) { return il8 ? (size_t)(f / 8) * 16 + 8 + f % 8 : (size_t)F + f; }
+
+// dot product of a weight row (T, global) with a row held in shared memory (fp32), 16 bytes per lane per load when `vec`
+template <typename T>
+__device__ __forceinline__ float row_dot(const T* __restrict__ w, const float* __restrict__ xs, int n, int lane, bool vec) {
+  constexpr int VEC = 16 / sizeof(T);
+  float acc = 0.f;
+  if (vec) {
+    for (int k = lane * VEC; k < n; k += 32 * VEC) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(w + k);
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) acc = fmaf(ldf(reinterpret_cast<const T*>(&raw) + v), xs[k + v], acc);
+    }
+  } else {
+    for (int k = lane; k < n; k += 32) acc = fmaf(ldf(w + k), xs[k], acc);
+  }
+  return warp_sum(acc);
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------
 // Mixture of experts, row form (few rows, and the 32-bit mode): every (row, chosen expert) streams that expert's matrices.
 //   moe_rows_up_kernel   act[m, k, f] = silu(W_gate[e] h_m)[f] * (W_up[e] h_m)[f],  e = ids[m, k]        one warp per f
 //   moe_rows_down_kernel y[m, d] = sum_k wts[m, k] * (W_down[e_k] act[m, k, :])[d]                       one warp per d
-// w_gu: [E][2 * F, D] (gate rows, then up rows of an expert); w_down: [E][D, F].
+// w_down: [E][D, F].
 // ---------------------------------------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void moe_rows_up_kernel(const T* __restrict__ h, int D, const T* __restrict__ w_gu, int F, const int* __restrict__ ids, int top,
+__global__ void moe_rows_up_kernel(const T* __restrict__ h, int D, const T* __restrict__ w_gu, int F, int il8, const int* __restrict__ ids, int top,
                                    T* __restrict__ act) {
-  extern __shared__ float hs[];                                // the row, fp32
+  extern __shared__ __align__(16) float hs[];                  // the row, fp32
   const int m = blockIdx.x, k = blockIdx.y;
   const int e = ids[(size_t)m * top + k];
   for (int d = threadIdx.x; d < D; d += blockDim.x) hs[d] = ldf(h + (size_t)m * D + d);
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-  const T* wg = w_gu + (size_t)e * 2 * F * D;
-  const T* wu = wg + (size_t)F * D;
+  const T* we = w_gu + (size_t)e * 2 * F * D;
+  const bool vec = D % (16 / sizeof(T)) == 0 && (reinterpret_cast<uintptr_t>(w_gu) & 15) == 0;
   for (int f = blockIdx.z * nw + warp; f < F; f += gridDim.z * nw) {
-    float g = 0.f, u = 0.f;
-    for (int d = lane; d < D; d += 32) {
-      g = fmaf(ldf(wg + (size_t)f * D + d), hs[d], g);
-      u = fmaf(ldf(wu + (size_t)f * D + d), hs[d], u);
-    }
-    g = warp_sum(g);
-    u = warp_sum(u);
+    const float g = row_dot(we + moe_gate_row(f, F, il8) * D, hs, D, lane, vec);
+    const float u = row_dot(we + moe_up_row(f, F, il8) * D, hs, D, lane, vec);
     if (lane == 0) stf(act + ((size_t)m * top + k) * F + f, siluf_(g) * u);
   }
 }
 template <typename T>
 __global__ void moe_rows_down_kernel(const T* __restrict__ act, int F, const T* __restrict__ w_down, int D, const int* __restrict__ ids,
                                      const float* __restrict__ wts, int top, float* __restrict__ y) {
-  extern __shared__ float as[];                                // [top][F] fp32
+  extern __shared__ __align__(16) float as[];                  // [top][F] fp32
   const int m = blockIdx.x;
   for (int i = threadIdx.x; i < top * F; i += blockDim.x) as[i] = ldf(act + (size_t)m * top * F + i);
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const bool vec = F % (16 / sizeof(T)) == 0 && (reinterpret_cast<uintptr_t>(w_down) & 15) == 0;
   for (int d = blockIdx.y * nw + warp; d < D; d += gridDim.y * nw) {
     float out = 0.f;
     for (int k = 0; k < top; ++k) {
       const T* wd = w_down + ((size_t)ids[(size_t)m * top + k] * D + d) * F;
-      float acc = 0.f;
-      for (int f = lane; f < F; f += 32) acc = fmaf(ldf(wd + f), as[k * F + f], acc);
-      out = fmaf(wts[(size_t)m * top + k], warp_sum(acc), out);
+      out = fmaf(wts[(size_t)m * top + k], row_dot(wd, as + k * F, F, lane, vec), out);
     }
     if (lane == 0) y[(size_t)m * D + d] = out;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// Mixture of experts, grouped form (many rows, bf16): the (row, expert) pairs are sorted by expert on the device, every expert's
+// run padded to whole 128-row tiles, and two tensor-core products run over the tiles with the expert's matrices chosen per tile.
+//   moe_plan_kernel    (one block)  counts -> padded run starts, tile -> expert map (-1 beyond the last run), cursors reset
+//   moe_scatter_kernel (one warp per pair) takes the pair's place in its expert's run, remembers it, copies the row there
+//   moe_combine_kernel y[m, :] = sum_k wts[m, k] * yg[place[m, k], :]
+// ints: counts[E], starts[E + 1], cursor[E], then tile_expert[n_tiles].  The order of pairs inside a run depends on scheduling; a
+// pair's result does not (rows of a product are independent).
+// ---------------------------------------------------------------------------------------------------------------------------
+__global__ void moe_count_kernel(const int* __restrict__ ids, int n_pairs, int* __restrict__ counts) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n_pairs) atomicAdd(counts + ids[i], 1);
+}
+__global__ void moe_plan_kernel(int* __restrict__ counts, int E, int tile_rows, int n_tiles, int* __restrict__ starts, int* __restrict__ cursor,
+                                int* __restrict__ tile_expert) {
+  __shared__ int s_total;
+  if (threadIdx.x == 0) {
+    int at = 0;
+    for (int e = 0; e < E; ++e) {
+      starts[e] = at;
+      at += (counts[e] + tile_rows - 1) / tile_rows * tile_rows;
+      cursor[e] = 0;
+    }
+    starts[E] = at;
+    s_total = at;
+  }
+  __syncthreads();
+  for (int t = threadIdx.x; t < n_tiles; t += blockDim.x) {
+    const int r = t * tile_rows;
+    int ex = -1;
+    if (r < s_total) {
+      int lo = 0, hi = E - 1;                                  // the last expert whose run starts at or before r and is not empty there
+      while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (starts[mid] <= r) lo = mid; else hi = mid - 1;
+      }
+      ex = lo;
+    }
+    tile_expert[t] = ex;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = 0;   // ready for the next layer
+}
+template <typename T>
+__global__ void moe_scatter_kernel(const T* __restrict__ h, int D, const int* __restrict__ ids, int n_pairs, int top, const int* __restrict__ starts,
+                                   int* __restrict__ cursor, int* __restrict__ place, T* __restrict__ xg) {
+  const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (i >= n_pairs) return;
+  int p = 0;
+  if (lane == 0) {
+    const int e = ids[i];
+    p = starts[e] + atomicAdd(cursor + e, 1);
+    place[i] = p;
+  }
+  p = __shfl_sync(0xffffffffu, p, 0);
+  const T* src = h + (size_t)(i / top) * D;
+  T* dst = xg + (size_t)p * D;
+  constexpr int VEC = 16 / sizeof(T);
+  if (D % VEC == 0) {
+    for (int d = lane * VEC; d < D; d += 32 * VEC) *reinterpret_cast<uint4*>(dst + d) = *reinterpret_cast<const uint4*>(src + d);
+  } else {
+    for (int d = lane; d < D; d += 32) dst[d] = src[d];
+  }
+}
+__global__ void moe_combine_kernel(const float* __restrict__ yg, const int* __restrict__ place, const float* __restrict__ wts, int top, int D,
+                                   float* __restrict__ y) {
+  const size_t m = blockIdx.x;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float acc = 0.f;
+    for (int k = 0; k < top; ++k) acc = fmaf(wts[m * top + k], yg[(size_t)place[m * top + k] * D + d], acc);
+    y[m * D + d] = acc;
   }
 }
 

@@ -219,4 +219,171 @@ __global__ void gqa_combine_kernel(const float* __restrict__ part, const Item* _
   }
 }
 
+// ===========================================================================================================================
+// Prompt attention on the tensor cores (bf16 serving path; requests that bring FLASH_MIN_ROWS rows or more; sizes whose rows are
+// whole 16-byte chunks: dk, dv multiples of 8, dk <= 256, dv <= 128).  One CTA = one tile of up to 64 consecutive rows of one
+// request x one query head.  Keys and values of the head's key/value group come straight from the paged pool by 16-byte cp.async
+// into two buffers each (the next 64 keys are in flight while these are multiplied); Q, K fragments by ldmatrix, V transposed on
+// the way into registers by ldmatrix.trans; scores by mma.sync.m16n8k16 (bf16 operands, fp32 accumulators), then in fp32: scale,
+// soft cap, distance penalty, mask, running max and sum.  The softmax weights enter the value product as a bf16 PAIR (high part +
+// remainder, two MMAs) so that they keep 16 mantissa bits.
+// ===========================================================================================================================
+struct GqaTile {
+  int row0;      // first packed row
+  int n_rows;    // <= 64 consecutive rows of one request
+  int pos0;      // position of row0
+  int slot;      // request
+};
+
+template <int DVT>   // value columns per warp row: DVT tiles of 8 (dv <= 8 * DVT)
+__global__ void __launch_bounds__(128)
+gqa_flash_kernel(const bf16* __restrict__ q16, const bf16* __restrict__ pool, Paging pg, const GqaTile* __restrict__ tiles, int H, int G, int dk, int dv,
+                 GqaScore sc, const float* __restrict__ gate, int gate_mode, int gate_ld, int gate_col0, bf16* __restrict__ out) {
+  extern __shared__ __align__(16) uint8_t gsm[];
+  const GqaTile tl = tiles[blockIdx.x];
+  const int h = blockIdx.y, g = h / (H / G);
+  const int DQP = (dk + 15) & ~15, QS = DQP + 8;
+  constexpr int VS = 8 * DVT + 8;
+  bf16* Qs = reinterpret_cast<bf16*>(gsm);          // [64][QS]
+  bf16* Ks = Qs + 64 * QS;                          // [2][64][QS]
+  bf16* Vs = Ks + 2 * 64 * QS;                      // [2][64][VS]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, t = lane & 3;
+  const uint4 zero4 = make_uint4(0, 0, 0, 0);
+  const int last = tl.pos0 + tl.n_rows - 1;
+  const int first = gqa_first_key(tl.pos0, sc.window, sc.chunk);
+  const int qc = DQP / 8;
+  const size_t rowlen = (size_t)G * (dk + dv);
+  const float r1 = sc.r1 ? __bfloat162float(static_cast<const bf16*>(sc.r1)[h]) : 0.f, r2 = sc.r1 ? __bfloat162float(static_cast<const bf16*>(sc.r2)[h]) : 0.f;
+
+  auto issue = [&](int j0, int bsel) {
+    bf16* kd = Ks + bsel * 64 * QS;
+    for (int e = threadIdx.x; e < 64 * qc; e += 128) {
+      const int r = e / qc, c = (e % qc) * 8, j = j0 + r;
+      bf16* dst = kd + r * QS + c;
+      if (j > last || c >= dk) *reinterpret_cast<uint4*>(dst) = zero4;
+      else cp_async16_b(dst, pool + pg.row(tl.slot, j) * rowlen + (size_t)g * dk + c);
+    }
+    bf16* vd = Vs + bsel * 64 * VS;
+    for (int e = threadIdx.x; e < 64 * DVT; e += 128) {
+      const int r = e / DVT, c = (e % DVT) * 8, j = j0 + r;
+      bf16* dst = vd + r * VS + c;
+      if (j > last || c >= dv) *reinterpret_cast<uint4*>(dst) = zero4;
+      else cp_async16_b(dst, pool + pg.row(tl.slot, j) * rowlen + (size_t)G * dk + (size_t)g * dv + c);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  for (int e = threadIdx.x; e < 64 * qc; e += 128) {
+    const int r = e / qc, c = (e % qc) * 8;
+    uint4 v = zero4;
+    if (r < tl.n_rows && c < dk) v = *reinterpret_cast<const uint4*>(q16 + ((size_t)(tl.row0 + r) * H + h) * dk + c);
+    *reinterpret_cast<uint4*>(Qs + r * QS + c) = v;
+  }
+  float o[DVT][4];
+#pragma unroll
+  for (int i = 0; i < DVT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float mx[2] = {-INFINITY, -INFINITY}, den[2] = {0.f, 0.f};
+  const int pos_lo = tl.pos0 + warp * 16 + gq, pos_hi = pos_lo + 8;
+  const int ntile = (last - first) / 64 + 1;
+  issue(first, 0);
+  for (int it = 0; it < ntile; ++it) {
+    const int j0 = first + it * 64, bsel = it & 1;
+    if (it + 1 < ntile) {
+      issue(j0 + 64, bsel ^ 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    const bf16* kt = Ks + bsel * 64 * QS;
+    const bf16* vt = Vs + bsel * 64 * VS;
+    float s[8][4];
+#pragma unroll
+    for (int n = 0; n < 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+    for (int k0 = 0; k0 < DQP; k0 += 16) {
+      uint32_t a[4];
+      ldsm_x4(a, Qs + (warp * 16 + (lane & 15)) * QS + k0 + (lane >> 4) * 8);
+#pragma unroll
+      for (int n = 0; n < 8; n += 2) {
+        uint32_t b[4];
+        ldsm_x4(b, kt + (n * 8 + (lane & 7) + ((lane >> 4) << 3)) * QS + k0 + ((lane >> 3) & 1) * 8);
+        mma_bf16_16816(s[n], a[0], a[1], a[2], a[3], b[0], b[1]);
+        mma_bf16_16816(s[n + 1], a[0], a[1], a[2], a[3], b[2], b[3]);
+      }
+    }
+    float tmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int n = 0; n < 8; ++n)
+#pragma unroll
+      for (int x = 0; x < 4; ++x) {
+        const int j = j0 + n * 8 + 2 * t + (x & 1), pos = (x < 2) ? pos_lo : pos_hi;
+        const bool vis = j <= last && gqa_visible(pos, j, sc.window, sc.chunk);
+        s[n][x] = vis ? gqa_adjust<bf16>(s[n][x], sc, r1, r2, pos - j) : -INFINITY;
+        tmax[x >> 1] = fmaxf(tmax[x >> 1], s[n][x]);
+      }
+    float corr[2], nmx[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 1));
+      tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 2));
+      nmx[r] = fmaxf(mx[r], tmax[r]);
+      corr[r] = (mx[r] == -INFINITY) ? 0.f : expf(mx[r] - nmx[r]);
+      mx[r] = nmx[r];
+    }
+    float psum[2] = {0.f, 0.f};
+#pragma unroll
+    for (int n = 0; n < 8; ++n)
+#pragma unroll
+      for (int x = 0; x < 4; ++x) {
+        const float p = (s[n][x] == -INFINITY) ? 0.f : expf(s[n][x] - nmx[x >> 1]);
+        s[n][x] = p;
+        psum[x >> 1] += p;
+      }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      psum[r] += __shfl_xor_sync(0xffffffffu, psum[r], 1);
+      psum[r] += __shfl_xor_sync(0xffffffffu, psum[r], 2);
+      den[r] = den[r] * corr[r] + psum[r];
+    }
+#pragma unroll
+    for (int i = 0; i < DVT; ++i) { o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1]; }
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {
+      uint32_t ah[4], al[4];
+#pragma unroll
+      for (int x = 0; x < 4; ++x) {
+        const float p0 = s[2 * kk + (x >> 1)][(x & 1) * 2], p1 = s[2 * kk + (x >> 1)][(x & 1) * 2 + 1];
+        const float h0 = __bfloat162float(__float2bfloat16_rn(p0)), h1 = __bfloat162float(__float2bfloat16_rn(p1));
+        ah[x] = pack_bf16x2(h0, h1);
+        al[x] = pack_bf16x2(p0 - h0, p1 - h1);
+      }
+#pragma unroll
+      for (int i = 0; i < DVT; i += 2) {
+        uint32_t b[4];
+        ldsm_x4_trans(b, vt + (kk * 16 + (lane & 15)) * VS + i * 8 + (lane >> 4) * 8);
+        mma_bf16_16816(o[i], ah[0], ah[1], ah[2], ah[3], b[0], b[1]);
+        mma_bf16_16816(o[i], al[0], al[1], al[2], al[3], b[0], b[1]);
+        mma_bf16_16816(o[i + 1], ah[0], ah[1], ah[2], ah[3], b[2], b[3]);
+        mma_bf16_16816(o[i + 1], al[0], al[1], al[2], al[3], b[2], b[3]);
+      }
+    }
+    __syncthreads();                                 // this buffer is refilled by the next iteration's issue
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int qi = warp * 16 + gq + r * 8;
+    if (qi >= tl.n_rows) continue;
+    const size_t m = tl.row0 + qi;
+    const float inv = 1.0f / den[r];
+    bf16* dst = out + m * ((size_t)H * dv) + (size_t)h * dv;
+#pragma unroll
+    for (int i = 0; i < DVT; ++i) {
+      const int c = i * 8 + 2 * t;
+      if (c < dv)
+        *reinterpret_cast<uint32_t*>(dst + c) = pack_bf16x2(o[i][r * 2] * inv * gqa_gate(gate, gate_mode, m, gate_ld, gate_col0, h, dv, c),
+                                                            o[i][r * 2 + 1] * inv * gqa_gate(gate, gate_mode, m, gate_ld, gate_col0, h, dv, c + 1));
+    }
+  }
+}
+
 }  // namespace xl

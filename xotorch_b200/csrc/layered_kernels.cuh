@@ -711,6 +711,15 @@ __global__ void store_rows_kernel(const bf16* __restrict__ src, T* __restrict__ 
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
     stf(dst + i, __bfloat162float(src[i]));
 }
+// rows of src [rows, cols] go to dst rows (r / 8) * 16 + half * 8 + r % 8: two matrices interleaved in groups of 8 rows
+template <typename T>
+__global__ void store_rows_interleaved8_kernel(const bf16* __restrict__ src, T* __restrict__ dst, int rows, int cols, int half) {
+  const size_t n = (size_t)rows * cols;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = i / cols, c = i % cols;
+    stf(dst + ((r / 8) * 16 + (size_t)half * 8 + r % 8) * cols + c, __bfloat162float(src[i]));
+  }
+}
 // synthetic weights: element i = mean + dev * (uniform in [-sqrt 3, sqrt 3)) from a counter hash — for benchmarks and smoke runs
 template <typename T>
 __global__ void fill_random_kernel(T* __restrict__ dst, size_t n, uint64_t seed, float mean, float dev) {

@@ -6,7 +6,9 @@
 // (cp.async.bulk.tensor.3d, SWIZZLE_128B; coordinates {k, row, batch}), a single thread issues tcgen05.mma.cta_group::1.kind::f16
 // into a tensor-memory accumulator, four warps read it back with tcgen05.ld and store it (fp32 or bf16, optionally relu(.)^2).
 // Rows beyond M, columns beyond N and the tail of K come from the tensor map's zero fill, so no size has to be a multiple of the
-// tile.  The PTX wrappers are those of the shard engine's prefill GEMM (prefill_tc.cuh); what differs is the operand layout
+// tile.  EPI 1: relu(.)^2; EPI 2: xIELU; EPI 3: the columns come in groups of 16 = 8 gate values followed by their 8 up values, and
+// C [*, N / 2] receives silu(gate) * up.  With `tile_batch` every row tile takes its B matrix from a list (grouped products: rows
+// sorted by expert).  The PTX wrappers are those of the shard engine's prefill GEMM (prefill_tc.cuh); what differs is the operand layout
 // (plain row-major weights, batched per-head products through the third coordinate), the epilogue and that EVERY wait is bounded:
 // a wait that expires sets *err and the CTA drains, frees its tensor memory and returns.
 #pragma once
@@ -38,6 +40,7 @@ struct LtcArgs {
   long ldc, c_batch;
   int* err;
   const __nv_bfloat16* epi;   // EPI 2: the two raw xIELU parameters
+  const int* tile_batch;      // not NULL: row tile t reads B's batch tile_batch[t] (A and C are not batched); a negative entry = the tile is empty
 };
 
 template <typename TC>
@@ -60,6 +63,8 @@ ltc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = blockIdx.x * LTC_M, n0 = blockIdx.y * NT, z = blockIdx.z;
   const int nkb = (a.K + LTC_BK - 1) / LTC_BK;
+  const int zb = a.tile_batch ? a.tile_batch[blockIdx.x] : z;
+  if (zb < 0) return;                                  // an empty tile of a grouped product: the whole CTA leaves before anything is set up
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < NS; ++i) { xb::mbar_init(&full[i], 1); xb::mbar_init(&empty[i], 1); }
@@ -83,7 +88,7 @@ ltc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       uint8_t* sa = base + (size_t)st * STAGE;
       xb::mbar_expect_tx(&full[st], STAGE);
       xb::tma_load_3d(sa, &tmA, kb * LTC_BK, m0, z, &full[st]);
-      xb::tma_load_3d(sa + A_BYTES, &tmB, kb * LTC_BK, n0, z, &full[st]);
+      xb::tma_load_3d(sa + A_BYTES, &tmB, kb * LTC_BK, n0, zb, &full[st]);
       issued = kb + 1;
     }
     if (!ok)   // gave up: let the copies still in flight land before the CTA's shared memory goes away
@@ -123,6 +128,23 @@ ltc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         const int n = n0 + c0;
         if (row >= a.M || n >= a.N) continue;
         float f[16];
+        if constexpr (EPI == 3) {                      // 8 gate values, then their 8 up values -> 8 outputs at columns n / 2 ..
+          const int no = n >> 1;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) f[j] = siluf_(__uint_as_float(v[j])) * __uint_as_float(v[j + 8]);
+          if (sizeof(TC) == 2 && a.ldc % 8 == 0 && (reinterpret_cast<uintptr_t>(a.C) & 15) == 0) {
+            uint32_t pk[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              __nv_bfloat162 h2 = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+              pk[j] = *reinterpret_cast<uint32_t*>(&h2);
+            }
+            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(crow) + no) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) ltc_store<TC>(crow + no + j, f[j]);
+          }
+        } else {
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
           f[j] = __uint_as_float(v[j]);
@@ -147,6 +169,7 @@ ltc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 #pragma unroll
           for (int j = 0; j < 16; ++j)
             if (n + j < a.N) ltc_store<TC>(crow + n + j, f[j]);
+        }
         }
       }
     }
