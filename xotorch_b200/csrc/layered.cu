@@ -140,6 +140,8 @@ struct xotb200_lm {
   float* moe_yg = nullptr;                             // grouped form: the experts' outputs [padded pairs, D]
   int* moe_plan = nullptr;                             // counts[E], starts[E + 1], cursor[E], place[rows * top], tile_expert[tiles]
   int moe_tiles_cap = 0;
+  float* dist_tab = nullptr;                           // prompt attention: distance penalties per head and distance, remade per layer
+  size_t dist_cap = 0;
   int max_conv = 0, max_top = 0, max_eff = 0, max_experts = 0;
   size_t final_norm_b = 0, pos_table = 0;
   void *h = nullptr, *cqn = nullptr, *qn = nullptr, *olat = nullptr, *oh = nullptr, *act = nullptr, *th = nullptr, *hw = nullptr;
@@ -870,12 +872,22 @@ static int gqa_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
       const int dqp = (dk + 15) & ~15, dvt = dv <= 64 ? 8 : 16;
       const size_t fsm = ((size_t)3 * 64 * (dqp + 8) + (size_t)2 * 64 * (8 * dvt + 8)) * 2;
       const dim3 grid(sp.n_gqa_tiles, H);
+      // distances a tile can meet: up to the longest request, less under a block or window rule (a 64-row tile reaches 63 further back)
+      int dist_n = sp.max_len;
+      if (s.chunk > 0) dist_n = std::min(dist_n, s.chunk + 64);
+      if (s.window > 0) dist_n = std::min(dist_n, s.window + 64);
+      if (s.dist_bias) {
+        if ((size_t)H * dist_n > e->dist_cap) { TRY(regrow(e->dist_tab, (size_t)H * dist_n * 4)); e->dist_cap = (size_t)H * dist_n; }
+        gqa_dist_table_kernel<<<cdiv((long)H * dist_n, 256), 256, 0, e->stream>>>(at<bf16>(e, L.r1), at<bf16>(e, L.r2), H, dist_n, e->dist_tab);
+        CK(cudaGetLastError());
+        e->launches++;
+      }
 #define LAUNCH_GQA_FLASH(DVT)                                                                                                              \
   do {                                                                                                                                     \
     auto kern = gqa_flash_kernel<DVT>;                                                                                                     \
     TRY(opt_in_smem(kern, fsm));                                                                                                           \
-    kern<<<grid, 128, fsm, e->stream>>>(static_cast<const bf16*>(e->q16), pool, pg, sp.gqa_tiles, H, G, dk, dv, sc, gate, s.out_gate, L.n_in, \
-                                        L.c_g, static_cast<bf16*>(e->oh));                                                                  \
+    kern<<<grid, 128, fsm, e->stream>>>(static_cast<const bf16*>(e->q16), pool, pg, sp.gqa_tiles, H, G, dk, dv, sc,                        \
+                                        s.dist_bias ? e->dist_tab : nullptr, dist_n, gate, s.out_gate, L.n_in, L.c_g, static_cast<bf16*>(e->oh)); \
   } while (0)
       if (dvt == 8) LAUNCH_GQA_FLASH(8);
       else LAUNCH_GQA_FLASH(16);
@@ -946,7 +958,12 @@ static int feed_forward(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
   T* h = static_cast<T*>(e->h);
   if (s.ff_kind == XOTB200_LM_FF_MOE) {
     const int E = s.experts, F = s.expert_ff, top = s.top;
-    moe_router_kernel<T><<<cdiv(M, 4), 128, (size_t)4 * (E + 32) * 4, e->stream>>>(h, D, at<T>(e, L.router), E, s.groups, s.groups_keep, top, e->moe_ids, e->moe_wts, M);
+    {
+      auto kern = moe_router_kernel<T>;
+      const size_t rsm = ((size_t)((D + 3) & ~3) + E) * 4;
+      TRY(opt_in_smem(kern, rsm));
+      kern<<<M, std::min(1024, std::max(64, cdiv(E, 2) * 32)), rsm, e->stream>>>(h, D, at<T>(e, L.router), E, s.groups, s.groups_keep, top, e->moe_ids, e->moe_wts, M);
+    }
     CK(cudaGetLastError());
     e->launches++;
     const int il8 = F % 8 == 0 ? 1 : 0;
@@ -977,14 +994,14 @@ static int feed_forward(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
     {
       auto kern = moe_rows_up_kernel<T>;
       TRY(opt_in_smem(kern, (size_t)D * 4));
-      kern<<<dim3(M, top, std::max(1, std::min(cdiv(F, 8), 64))), 256, (size_t)D * 4, e->stream>>>(h, D, at<T>(e, L.w_gu), F, il8, e->moe_ids, top, static_cast<T*>(e->mact));
+      kern<<<dim3(M, top, std::max(1, std::min(cdiv(F, 8), M <= 16 ? 1024 : 16))), 256, (size_t)D * 4, e->stream>>>(h, D, at<T>(e, L.w_gu), F, il8, e->moe_ids, top, static_cast<T*>(e->mact));
       CK(cudaGetLastError());
       e->launches++;
     }
     {
       auto kern = moe_rows_down_kernel<T>;
       TRY(opt_in_smem(kern, (size_t)top * F * 4));
-      kern<<<dim3(M, std::max(1, std::min(cdiv(D, 8), 64))), 256, (size_t)top * F * 4, e->stream>>>(static_cast<T*>(e->mact), F, at<T>(e, L.w_edown), D, e->moe_ids, e->moe_wts,
+      kern<<<dim3(M, std::max(1, std::min(cdiv(D, 8), M <= 16 ? 1024 : 16))), 256, (size_t)top * F * 4, e->stream>>>(static_cast<T*>(e->mact), F, at<T>(e, L.w_edown), D, e->moe_ids, e->moe_wts,
                                                                                                    top, e->y);
       CK(cudaGetLastError());
       e->launches++;
@@ -1197,7 +1214,7 @@ int xotb200_lm_destroy(xotb200_lm* e) {
   free_state(e);
   for (auto& L : e->layers)
     if (L.freqs) cudaFree(L.freqs);
-  void* ptrs[] = {e->moe_xg, e->moe_yg, e->moe_plan, e->dkk, e->drr, e->cvb, e->moe_ids, e->moe_wts, e->mact, e->du, e->dau, e->part, e->q16, e->cbuf, e->knx, e->vxx, e->blob, e->d_stage, e->x, e->y, e->proj, e->qraw, e->qfull, e->wlog, e->oraw, e->logits, e->h, e->cqn, e->qn, e->olat, e->oh, e->act,
+  void* ptrs[] = {e->dist_tab, e->moe_xg, e->moe_yg, e->moe_plan, e->dkk, e->drr, e->cvb, e->moe_ids, e->moe_wts, e->mact, e->du, e->dau, e->part, e->q16, e->cbuf, e->knx, e->vxx, e->blob, e->d_stage, e->x, e->y, e->proj, e->qraw, e->qfull, e->wlog, e->oraw, e->logits, e->h, e->cqn, e->qn, e->olat, e->oh, e->act,
                   e->th, e->hw, e->d_argmax, e->trace_buf};
   for (void* p : ptrs)
     if (p) cudaFree(p);

@@ -144,29 +144,98 @@ __global__ void gated_delta_prepare_kernel(const float* __restrict__ cv, int C, 
   }
 }
 
+// dot product of a weight row (T, global) with a row held in shared memory (fp32), 16 bytes per lane per load when `vec`
+template <typename T>
+__device__ __forceinline__ float row_dot(const T* __restrict__ w, const float* __restrict__ xs, int n, int lane, bool vec) {
+  constexpr int VEC = 16 / sizeof(T);
+  float acc = 0.f;
+  if (vec) {
+    for (int k = lane * VEC; k < n; k += 32 * VEC) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(w + k);
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) acc = fmaf(ldf(reinterpret_cast<const T*>(&raw) + v), xs[k + v], acc);
+    }
+  } else {
+    for (int k = lane; k < n; k += 32) acc = fmaf(ldf(w + k), xs[k], acc);
+  }
+  return warp_sum(acc);
+}
+
+// two rows at once (w0 . x0 and w1 . x1): twice the loads in flight
+template <typename T>
+__device__ __forceinline__ void row_dot2(const T* __restrict__ w0, const T* __restrict__ w1, const float* __restrict__ x0, const float* __restrict__ x1,
+                                         int n, int lane, bool vec, float& r0, float& r1) {
+  constexpr int VEC = 16 / sizeof(T);
+  float a0 = 0.f, a1 = 0.f;
+  if (vec) {
+    for (int k = lane * VEC; k < n; k += 64 * VEC) {
+      const int k2 = k + 32 * VEC;
+      const uint4 z = make_uint4(0, 0, 0, 0);
+      const uint4 p0 = *reinterpret_cast<const uint4*>(w0 + k), p1 = *reinterpret_cast<const uint4*>(w1 + k);
+      const uint4 q0 = k2 < n ? *reinterpret_cast<const uint4*>(w0 + k2) : z, q1 = k2 < n ? *reinterpret_cast<const uint4*>(w1 + k2) : z;
+      const int kk = k2 < n ? k2 : k;                  // past the end the weights read as zero; the index stays inside x
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) {
+        a0 = fmaf(ldf(reinterpret_cast<const T*>(&p0) + v), x0[k + v], a0);
+        a1 = fmaf(ldf(reinterpret_cast<const T*>(&p1) + v), x1[k + v], a1);
+        a0 = fmaf(ldf(reinterpret_cast<const T*>(&q0) + v), x0[kk + v], a0);
+        a1 = fmaf(ldf(reinterpret_cast<const T*>(&q1) + v), x1[kk + v], a1);
+      }
+    }
+  } else {
+    for (int k = lane; k < n; k += 32) { a0 = fmaf(ldf(w0 + k), x0[k], a0); a1 = fmaf(ldf(w1 + k), x1[k], a1); }
+  }
+  r0 = warp_sum(a0);
+  r1 = warp_sum(a1);
+}
+
+// four rows at once
+template <typename T>
+__device__ __forceinline__ void row_dot4(const T* const (&w)[4], const float* const (&x)[4], int n, int lane, bool vec, float (&r)[4]) {
+  constexpr int VEC = 16 / sizeof(T);
+  float a[4] = {0.f, 0.f, 0.f, 0.f};
+  if (vec) {
+    for (int k = lane * VEC; k < n; k += 32 * VEC) {
+      uint4 p[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) p[i] = *reinterpret_cast<const uint4*>(w[i] + k);
+#pragma unroll
+      for (int v = 0; v < VEC; ++v)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) a[i] = fmaf(ldf(reinterpret_cast<const T*>(&p[i]) + v), x[i][k + v], a[i]);
+    }
+  } else {
+    for (int k = lane; k < n; k += 32)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = fmaf(ldf(w[i] + k), x[i][k], a[i]);
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) r[i] = warp_sum(a[i]);
+}
+
 // ---------------------------------------------------------------------------------------------------------------------------
 // Mixture of experts, router: logits z = W_r h in fp32 (h in T), scores s = softmax(z) over all E experts; experts form `groups`
 // equal groups of neighbours, a group's score is its best expert's, only experts of the `keep` best groups can be chosen; the
 // `top` best of those are the token's experts, weighted by their s (not renormalised).  Ties go to the lower index.
-// One warp per row; dynamic shared memory: warps * E floats.
+// One block per row (its warps share the experts' logits, warp 0 selects); dynamic shared memory: D + E floats.
 // ---------------------------------------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void moe_router_kernel(const T* __restrict__ h, int D, const T* __restrict__ w_router, int E, int groups, int keep, int top,
                                   int* __restrict__ ids, float* __restrict__ wts, int M) {
-  extern __shared__ float rsm[];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m = blockIdx.x * (blockDim.x >> 5) + warp;
-  if (m >= M) return;
-  float* s = rsm + (size_t)warp * (E + 32);                    // [E] scores, then [32] group flags scratch
-  const T* hr = h + (size_t)m * D;
-  for (int e = 0; e < E; ++e) {
-    const T* wr = w_router + (size_t)e * D;
-    float acc = 0.f;
-    for (int d = lane; d < D; d += 32) acc = fmaf(ldf(hr + d), ldf(wr + d), acc);
-    acc = warp_sum(acc);
-    if (lane == 0) s[e] = acc;
+  extern __shared__ __align__(16) float rsm[];                 // [D] the row (fp32), then [E] scores
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const int m = blockIdx.x;
+  float* hs = rsm;
+  float* s = rsm + ((D + 3) & ~3);
+  for (int d = threadIdx.x; d < D; d += blockDim.x) hs[d] = ldf(h + (size_t)m * D + d);
+  __syncthreads();
+  const bool vec = D % (16 / sizeof(T)) == 0 && (reinterpret_cast<uintptr_t>(w_router) & 15) == 0;
+  for (int e = warp; e < E; e += nw) {                         // the warps share the experts; logits in fp32
+    const float z = row_dot(w_router + (size_t)e * D, hs, D, lane, vec);
+    if (lane == 0) s[e] = z;
   }
-  __syncwarp();
+  __syncthreads();
+  if (warp != 0) return;
   float mx = -INFINITY;
   for (int e = lane; e < E; e += 32) mx = fmaxf(mx, s[e]);
   mx = warp_max(mx);
@@ -214,23 +283,6 @@ __global__ void moe_router_kernel(const T* __restrict__ h, int D, const T* __res
 __device__ __host__ __forceinline__ size_t moe_gate_row(int f, int F, int il8) { return il8 ? (size_t)(f / 8) * 16 + f % 8 : (size_t)f; }
 __device__ __host__ __forceinline__ size_t moe_up_row(int f, int F, int il8) { return il8 ? (size_t)(f / 8) * 16 + 8 + f % 8 : (size_t)F + f; }
 
-// dot product of a weight row (T, global) with a row held in shared memory (fp32), 16 bytes per lane per load when `vec`
-template <typename T>
-__device__ __forceinline__ float row_dot(const T* __restrict__ w, const float* __restrict__ xs, int n, int lane, bool vec) {
-  constexpr int VEC = 16 / sizeof(T);
-  float acc = 0.f;
-  if (vec) {
-    for (int k = lane * VEC; k < n; k += 32 * VEC) {
-      const uint4 raw = *reinterpret_cast<const uint4*>(w + k);
-#pragma unroll
-      for (int v = 0; v < VEC; ++v) acc = fmaf(ldf(reinterpret_cast<const T*>(&raw) + v), xs[k + v], acc);
-    }
-  } else {
-    for (int k = lane; k < n; k += 32) acc = fmaf(ldf(w + k), xs[k], acc);
-  }
-  return warp_sum(acc);
-}
-
 // ---------------------------------------------------------------------------------------------------------------------------
 // Mixture of experts, row form (few rows, and the 32-bit mode): every (row, chosen expert) streams that expert's matrices.
 //   moe_rows_up_kernel   act[m, k, f] = silu(W_gate[e] h_m)[f] * (W_up[e] h_m)[f],  e = ids[m, k]        one warp per f
@@ -249,8 +301,8 @@ __global__ void moe_rows_up_kernel(const T* __restrict__ h, int D, const T* __re
   const T* we = w_gu + (size_t)e * 2 * F * D;
   const bool vec = D % (16 / sizeof(T)) == 0 && (reinterpret_cast<uintptr_t>(w_gu) & 15) == 0;
   for (int f = blockIdx.z * nw + warp; f < F; f += gridDim.z * nw) {
-    const float g = row_dot(we + moe_gate_row(f, F, il8) * D, hs, D, lane, vec);
-    const float u = row_dot(we + moe_up_row(f, F, il8) * D, hs, D, lane, vec);
+    float g, u;
+    row_dot2(we + moe_gate_row(f, F, il8) * D, we + moe_up_row(f, F, il8) * D, hs, hs, D, lane, vec, g, u);
     if (lane == 0) stf(act + ((size_t)m * top + k) * F + f, siluf_(g) * u);
   }
 }
@@ -265,10 +317,25 @@ __global__ void moe_rows_down_kernel(const T* __restrict__ act, int F, const T* 
   const bool vec = F % (16 / sizeof(T)) == 0 && (reinterpret_cast<uintptr_t>(w_down) & 15) == 0;
   for (int d = blockIdx.y * nw + warp; d < D; d += gridDim.y * nw) {
     float out = 0.f;
-    for (int k = 0; k < top; ++k) {
-      const T* wd = w_down + ((size_t)ids[(size_t)m * top + k] * D + d) * F;
-      out = fmaf(wts[(size_t)m * top + k], row_dot(wd, as + k * F, F, lane, vec), out);
+    int k = 0;
+    for (; k + 3 < top; k += 4) {                      // the experts of a row four by four, then two by two, in their order
+      const T* w4[4];
+      const float* x4[4];
+      float r4[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { w4[i] = w_down + ((size_t)ids[(size_t)m * top + k + i] * D + d) * F; x4[i] = as + (k + i) * F; }
+      row_dot4(w4, x4, F, lane, vec, r4);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) out = fmaf(wts[(size_t)m * top + k + i], r4[i], out);
     }
+    for (; k + 1 < top; k += 2) {
+      float r0, r1;
+      row_dot2(w_down + ((size_t)ids[(size_t)m * top + k] * D + d) * F, w_down + ((size_t)ids[(size_t)m * top + k + 1] * D + d) * F, as + k * F,
+               as + (k + 1) * F, F, lane, vec, r0, r1);
+      out = fmaf(wts[(size_t)m * top + k], r0, out);
+      out = fmaf(wts[(size_t)m * top + k + 1], r1, out);
+    }
+    if (k < top) out = fmaf(wts[(size_t)m * top + k], row_dot(w_down + ((size_t)ids[(size_t)m * top + k] * D + d) * F, as + k * F, F, lane, vec), out);
     if (lane == 0) y[(size_t)m * D + d] = out;
   }
 }

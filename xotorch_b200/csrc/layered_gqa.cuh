@@ -32,6 +32,16 @@ __device__ __forceinline__ float gqa_adjust(float dot, const GqaScore& sc, float
   if (sc.r1) s -= r1 * log1pf(r2 * (float)dist);
   return s;
 }
+// the same in the tensor-core prompt kernel: fp32 with the fast exponential and division units (tanh x = (e^2x - 1) / (e^2x + 1))
+__device__ __forceinline__ float gqa_adjust_fast(float dot, const GqaScore& sc, float inv_cap, const float* __restrict__ dist_penalty, int dist) {
+  float s = dot * sc.scale;
+  if (sc.cap > 0.f) {
+    const float t = __expf(2.0f * fminf(fmaxf(s * inv_cap, -15.f), 15.f));
+    s = sc.cap * __fdividef(t - 1.0f, t + 1.0f);
+  }
+  if (dist_penalty) s -= __ldg(dist_penalty + dist);          // r1 * ln(1 + r2 * dist), tabulated per head
+  return s;
+}
 __device__ __forceinline__ bool gqa_visible(int pos, int j, int window, int chunk) {
   return j <= pos && (window == 0 || pos - j < window) && (chunk == 0 || j / chunk == pos / chunk);
 }
@@ -228,6 +238,15 @@ __global__ void gqa_combine_kernel(const float* __restrict__ part, const Item* _
 // soft cap, distance penalty, mask, running max and sum.  The softmax weights enter the value product as a bf16 PAIR (high part +
 // remainder, two MMAs) so that they keep 16 mantissa bits.
 // ===========================================================================================================================
+// dist_table[a][d] = r1[a] * ln(1 + r2[a] * d) for d < n: the distance penalty of head a, made once per step and layer so that the
+// prompt kernel reads it instead of taking a logarithm per score
+__global__ void gqa_dist_table_kernel(const bf16* __restrict__ r1, const bf16* __restrict__ r2, int H, int n, float* __restrict__ table) {
+  const size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+  if (i >= (size_t)H * n) return;
+  const int a = (int)(i / n), d = (int)(i % n);
+  table[i] = __bfloat162float(r1[a]) * log1pf(__bfloat162float(r2[a]) * (float)d);
+}
+
 struct GqaTile {
   int row0;      // first packed row
   int n_rows;    // <= 64 consecutive rows of one request
@@ -238,9 +257,11 @@ struct GqaTile {
 template <int DVT>   // value columns per warp row: DVT tiles of 8 (dv <= 8 * DVT)
 __global__ void __launch_bounds__(128)
 gqa_flash_kernel(const bf16* __restrict__ q16, const bf16* __restrict__ pool, Paging pg, const GqaTile* __restrict__ tiles, int H, int G, int dk, int dv,
-                 GqaScore sc, const float* __restrict__ gate, int gate_mode, int gate_ld, int gate_col0, bf16* __restrict__ out) {
+                 GqaScore sc, const float* __restrict__ dist_table, int dist_n, const float* __restrict__ gate, int gate_mode, int gate_ld, int gate_col0,
+                 bf16* __restrict__ out) {
   extern __shared__ __align__(16) uint8_t gsm[];
-  const GqaTile tl = tiles[blockIdx.x];
+  __shared__ size_t krow[2][64];                    // pool rows of the keys of the tile in flight / in use
+  const GqaTile tl = tiles[gridDim.x - 1 - blockIdx.x];   // later tiles of a request see more keys: the long ones start first
   const int h = blockIdx.y, g = h / (H / G);
   const int DQP = (dk + 15) & ~15, QS = DQP + 8;
   constexpr int VS = 8 * DVT + 8;
@@ -253,22 +274,26 @@ gqa_flash_kernel(const bf16* __restrict__ q16, const bf16* __restrict__ pool, Pa
   const int first = gqa_first_key(tl.pos0, sc.window, sc.chunk);
   const int qc = DQP / 8;
   const size_t rowlen = (size_t)G * (dk + dv);
-  const float r1 = sc.r1 ? __bfloat162float(static_cast<const bf16*>(sc.r1)[h]) : 0.f, r2 = sc.r1 ? __bfloat162float(static_cast<const bf16*>(sc.r2)[h]) : 0.f;
+  const float* dtab = dist_table ? dist_table + (size_t)h * dist_n : nullptr;
 
+  // the page walk is done once per key (64 threads), then every thread copies 16-byte pieces from the rows it names
+  auto locate = [&](int j0, int bsel) {
+    if (threadIdx.x < 64) krow[bsel][threadIdx.x] = j0 + (int)threadIdx.x <= last ? pg.row(tl.slot, j0 + threadIdx.x) * rowlen : 0;
+  };
   auto issue = [&](int j0, int bsel) {
     bf16* kd = Ks + bsel * 64 * QS;
     for (int e = threadIdx.x; e < 64 * qc; e += 128) {
       const int r = e / qc, c = (e % qc) * 8, j = j0 + r;
       bf16* dst = kd + r * QS + c;
       if (j > last || c >= dk) *reinterpret_cast<uint4*>(dst) = zero4;
-      else cp_async16_b(dst, pool + pg.row(tl.slot, j) * rowlen + (size_t)g * dk + c);
+      else cp_async16_b(dst, pool + krow[bsel][r] + (size_t)g * dk + c);
     }
     bf16* vd = Vs + bsel * 64 * VS;
     for (int e = threadIdx.x; e < 64 * DVT; e += 128) {
       const int r = e / DVT, c = (e % DVT) * 8, j = j0 + r;
       bf16* dst = vd + r * VS + c;
       if (j > last || c >= dv) *reinterpret_cast<uint4*>(dst) = zero4;
-      else cp_async16_b(dst, pool + pg.row(tl.slot, j) * rowlen + (size_t)G * dk + (size_t)g * dv + c);
+      else cp_async16_b(dst, pool + krow[bsel][r] + (size_t)G * dk + (size_t)g * dv + c);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
@@ -284,7 +309,13 @@ gqa_flash_kernel(const bf16* __restrict__ q16, const bf16* __restrict__ pool, Pa
   for (int i = 0; i < DVT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   float mx[2] = {-INFINITY, -INFINITY}, den[2] = {0.f, 0.f};
   const int pos_lo = tl.pos0 + warp * 16 + gq, pos_hi = pos_lo + 8;
+  // visible keys of this thread's two rows: [lo, pos] (the divisions of the block rule are done once, here)
+  const int vis_lo[2] = {gqa_first_key(pos_lo, sc.window, sc.chunk), gqa_first_key(pos_hi, sc.window, sc.chunk)};
+  const float inv_cap = sc.cap > 0.f ? 1.0f / sc.cap : 0.f;
   const int ntile = (last - first) / 64 + 1;
+  locate(first, 0);
+  locate(first + 64, 1);
+  __syncthreads();
   issue(first, 0);
   for (int it = 0; it < ntile; ++it) {
     const int j0 = first + it * 64, bsel = it & 1;
@@ -295,6 +326,7 @@ gqa_flash_kernel(const bf16* __restrict__ q16, const bf16* __restrict__ pool, Pa
       asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     __syncthreads();
+    locate(j0 + 128, bsel);                          // krow[bsel] was last read by the issue of this tile; the next reader is two barriers away
     const bf16* kt = Ks + bsel * 64 * QS;
     const bf16* vt = Vs + bsel * 64 * VS;
     float s[8][4];
@@ -317,8 +349,8 @@ gqa_flash_kernel(const bf16* __restrict__ q16, const bf16* __restrict__ pool, Pa
 #pragma unroll
       for (int x = 0; x < 4; ++x) {
         const int j = j0 + n * 8 + 2 * t + (x & 1), pos = (x < 2) ? pos_lo : pos_hi;
-        const bool vis = j <= last && gqa_visible(pos, j, sc.window, sc.chunk);
-        s[n][x] = vis ? gqa_adjust<bf16>(s[n][x], sc, r1, r2, pos - j) : -INFINITY;
+        const bool vis = j <= last && j <= pos && j >= vis_lo[x >> 1];
+        s[n][x] = vis ? gqa_adjust_fast(s[n][x], sc, inv_cap, dtab, pos - j) : -INFINITY;
         tmax[x >> 1] = fmaxf(tmax[x >> 1], s[n][x]);
       }
     float corr[2], nmx[2];
@@ -327,7 +359,7 @@ gqa_flash_kernel(const bf16* __restrict__ q16, const bf16* __restrict__ pool, Pa
       tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 1));
       tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 2));
       nmx[r] = fmaxf(mx[r], tmax[r]);
-      corr[r] = (mx[r] == -INFINITY) ? 0.f : expf(mx[r] - nmx[r]);
+      corr[r] = (mx[r] == -INFINITY) ? 0.f : __expf(mx[r] - nmx[r]);
       mx[r] = nmx[r];
     }
     float psum[2] = {0.f, 0.f};
@@ -335,7 +367,7 @@ gqa_flash_kernel(const bf16* __restrict__ q16, const bf16* __restrict__ pool, Pa
     for (int n = 0; n < 8; ++n)
 #pragma unroll
       for (int x = 0; x < 4; ++x) {
-        const float p = (s[n][x] == -INFINITY) ? 0.f : expf(s[n][x] - nmx[x >> 1]);
+        const float p = (s[n][x] == -INFINITY) ? 0.f : __expf(s[n][x] - nmx[x >> 1]);
         s[n][x] = p;
         psum[x >> 1] += p;
       }
