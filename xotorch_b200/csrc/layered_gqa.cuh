@@ -39,7 +39,7 @@ __device__ __forceinline__ float gqa_adjust_fast(float dot, const GqaScore& sc, 
     const float t = __expf(2.0f * fminf(fmaxf(s * inv_cap, -15.f), 15.f));
     s = sc.cap * __fdividef(t - 1.0f, t + 1.0f);
   }
-  if (dist_penalty) s -= __ldg(dist_penalty + dist);          // r1 * ln(1 + r2 * dist), tabulated per head
+  if (dist_penalty) s -= dist_penalty[dist];                   // r1 * ln(1 + r2 * distance), tabulated per head; the caller's index
   return s;
 }
 __device__ __forceinline__ bool gqa_visible(int pos, int j, int window, int chunk) {
@@ -261,6 +261,7 @@ gqa_flash_kernel(const bf16* __restrict__ q16, const bf16* __restrict__ pool, Pa
                  bf16* __restrict__ out) {
   extern __shared__ __align__(16) uint8_t gsm[];
   __shared__ size_t krow[2][64];                    // pool rows of the keys of the tile in flight / in use
+  __shared__ float dpen[2][128];                    // distance penalties a (64 rows x 64 keys) tile can meet: distance = dbase + index
   const GqaTile tl = tiles[gridDim.x - 1 - blockIdx.x];   // later tiles of a request see more keys: the long ones start first
   const int h = blockIdx.y, g = h / (H / G);
   const int DQP = (dk + 15) & ~15, QS = DQP + 8;
@@ -319,6 +320,10 @@ gqa_flash_kernel(const bf16* __restrict__ q16, const bf16* __restrict__ pool, Pa
   issue(first, 0);
   for (int it = 0; it < ntile; ++it) {
     const int j0 = first + it * 64, bsel = it & 1;
+    if (dtab) {                                      // distances pos0 - (j0 + 63) + index; negative ones belong to keys after the row (masked)
+      const int d = tl.pos0 - j0 - 63 + (int)threadIdx.x;
+      dpen[bsel][threadIdx.x] = d >= 0 && d < dist_n ? dtab[d] : 0.f;
+    }
     if (it + 1 < ntile) {
       issue(j0 + 64, bsel ^ 1);
       asm volatile("cp.async.wait_group 1;" ::: "memory");
@@ -350,7 +355,7 @@ gqa_flash_kernel(const bf16* __restrict__ q16, const bf16* __restrict__ pool, Pa
       for (int x = 0; x < 4; ++x) {
         const int j = j0 + n * 8 + 2 * t + (x & 1), pos = (x < 2) ? pos_lo : pos_hi;
         const bool vis = j <= last && j <= pos && j >= vis_lo[x >> 1];
-        s[n][x] = vis ? gqa_adjust_fast(s[n][x], sc, inv_cap, dtab, pos - j) : -INFINITY;
+        s[n][x] = vis ? gqa_adjust_fast(s[n][x], sc, inv_cap, dtab ? dpen[bsel] : nullptr, (pos - tl.pos0) - (j - j0) + 63) : -INFINITY;
         tmax[x >> 1] = fmaxf(tmax[x >> 1], s[n][x]);
       }
     float corr[2], nmx[2];
