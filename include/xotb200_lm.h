@@ -8,7 +8,14 @@
  *                               all heads; options: query through a normed latent, rotation layout, sliding window, output gate;
  *                               state = the paged latent cache;
  *   XOTB200_LM_MIX_DELTA_RULE   generalised delta-rule recurrence with per-channel decay and removal rate;
- *                               state = one fp32 matrix per head, request and layer.
+ *                               state = one fp32 matrix per head, request and layer;
+ *   XOTB200_LM_MIX_ATTENTION    grouped-query attention over a paged cache of (normed) keys and values; options: projection
+ *                               biases, query/key norm, soft cap, logarithmic distance penalty, sliding window, block-local mask,
+ *                               output gate per head or per entry, keys/values borrowed from an earlier layer;
+ *   XOTB200_LM_MIX_GATED_DELTA  delta rule with one decay per head behind short causal convolutions;
+ *                               state = fp32 matrix per head + the convolutions' last inputs.
+ * A layer wraps its sublayers in grouped RMS norms before and after them, or reads the stream itself and closes with a layer norm
+ * (xotb200_lm_cfg.block); its feed-forward is dense (relu^2 or xIELU) or a mixture of gated experts (xotb200_lm_layer.ff_kind).
  * Every size and constant of a layer is a field of xotb200_lm_layer, so a model family is a table of layers, not code.
  *
  * Serving model: requests live in SLOTS (0 .. max_requests-1).  A step (xotb200_lm_step) takes a packed batch — for each

@@ -3,8 +3,8 @@
 //   model     : a table of layers (xotb200_lm_layer); weights in ONE blob of T (bf16 or fp32), input projections of a mixer that
 //               read the same normed input are stored as one concatenated matrix so they are one product;
 //   loader    : strict safetensors reader (mmap -> device staging -> widen/copy kernel into the blob);
-//   state     : paged latent cache (one pool per attention layer, page table per slot, host free list) + fp32 recurrent states
-//               per slot; slots are emptied and reused, pages return to the pool;
+//   state     : paged cache (one pool per attention layer that owns keys/values or latents, page table per slot, host free list)
+//               + fp32 recurrent states and convolution inputs per slot; slots are emptied and reused, pages return to the pool;
 //   step      : a packed batch of rows through the layers on one stream (kernels in layered_kernels.cuh), logits / argmax of the
 //               wanted rows back to the host.
 #include <cuda_runtime.h>
