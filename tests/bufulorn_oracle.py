@@ -25,10 +25,6 @@ def layer_norm(x: Tensor, w: Tensor, b: Tensor, eps: float) -> Tensor:
   return (x - mu) / torch.sqrt(var + eps) * w + b
 
 
-def gelu_tanh(z: Tensor) -> Tensor:
-  return 0.5 * z * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (z + 0.044715 * z ** 3)))
-
-
 def xielu(z: Tensor, p: Tensor, q: Tensor) -> Tensor:
   """two-sided activation with learned curvatures: a parabola on the right, a saturating exponential on the left"""
   right = F.softplus(p) * z * z + 0.5 * z
@@ -137,7 +133,7 @@ def route(h: Tensor, w_router: Tensor, r: dict) -> Tuple[Tensor, Tensor]:
   """chosen experts [T, top] and their weights: softmax over all experts, only experts of the `keep` best groups (a group's
   score is its best expert's) may be chosen, weights are the raw scores"""
   E, top = r["experts"], r["top"]
-  s = torch.softmax((h @ w_router.T).float(), dim=-1)
+  s = torch.softmax(h @ w_router.T, dim=-1)
   allowed = torch.ones_like(s, dtype=torch.bool)
   gr = r.get("groups")
   if gr and gr["count"] > 1:
@@ -153,10 +149,12 @@ def route(h: Tensor, w_router: Tensor, r: dict) -> Tuple[Tensor, Tensor]:
 def moe_ff(h: Tensor, W: Dict[str, Tensor], mlp: dict) -> Tensor:
   idx, wt = route(h, W["router"], mlp["router"])
   out = torch.zeros(h.shape[0], W["e0.down"].shape[0], dtype=h.dtype)
-  for t in range(h.shape[0]):
-    for e, w in zip(idx[t].tolist(), wt[t]):
-      a = F.silu(W[f"e{e}.gate"] @ h[t]) * (W[f"e{e}.up"] @ h[t])
-      out[t] += w.to(h.dtype) * (W[f"e{e}.down"] @ a)
+  for e in range(mlp["router"]["experts"]):                      # expert by expert: the rows that chose it, with their weight for it
+    rows, slot = (idx == e).nonzero(as_tuple=True)
+    if rows.numel():
+      x = h[rows]
+      a = F.silu(x @ W[f"e{e}.gate"].T) * (x @ W[f"e{e}.up"].T)
+      out[rows] += wt[rows, slot].to(h.dtype)[:, None] * (a @ W[f"e{e}.down"].T)
   return out
 
 

@@ -48,18 +48,18 @@ def zokuvik_config(s: dict):
 
 # Bufulorn shapes at the same widths: value heads x size of the delta layers as above, half as many query/key heads; attention
 # with 4 query heads per key/value head; 16 experts of a quarter of the dense inner size, 4 per token (as many active weights as
-# the dense layers), in 4 groups of which 2 are kept; blocks of 1024 positions
+# the dense layers), in 8 groups of which 4 are kept; blocks of 1024 positions
 BUFULORN = {
   "small": dict(heads=16, kv_heads=4, dim=64, vdim=64, dheads=16, dkv=8, ddim=64, dvdim=64),
   "medium": dict(heads=16, kv_heads=4, dim=128, vdim=128, dheads=32, dkv=16, ddim=64, dvdim=64),
   "large": dict(heads=32, kv_heads=8, dim=128, vdim=128, dheads=32, dkv=16, ddim=128, dvdim=128),
 }
-EXPERTS, TOP, GROUPS, KEEP, TAPS = 16, 4, 4, 2, 4
+EXPERTS, TOP, GROUPS, KEEP, TAPS = 16, 4, 8, 4, 4
 
 
 def bufulorn_config(s: dict, b: dict, context: int):
   def att(src, mlp):
-    m = {"heads": b["heads"], "kv_heads": b["kv_heads"], "dim": b["dim"], "vdim": b["vdim"], "scale": float(b["dim"] ** -0.5), "softcap": 50.0,
+    m = {"heads": b["heads"], "kv_heads": b["kv_heads"], "dim": b["dim"], "vdim": b["vdim"], "scale": float(b["dim"] ** -0.5), "softcap": 30.0,
          "mask": {"size": WINDOW}}
     if src is not None:
       m["kv_from"] = src
