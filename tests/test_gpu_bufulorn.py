@@ -487,35 +487,36 @@ def random_model(seed):
   return config(layers, width=width, vocab=pick(50, 131), max_positions=400)
 
 
-def rows_ok(got, ref, dtype):
-  """every row within the tolerance; in bfloat16 a few rows may leave it when a router score pair lies closer than the rounding of
-  the router's input (another expert is then chosen legitimately) — but only a few, and the typical row stays tight"""
+def row_errors(got, ref):
   d = got.astype(np.float64) - ref
   d = d - d.mean(axis=-1, keepdims=True)
   r = ref - ref.mean(axis=-1, keepdims=True)
-  e = np.sqrt((d * d).mean(-1)) / np.sqrt((r * r).mean(-1) + 1e-30)
-  if dtype == "float32":
-    return e.max() < TOL[dtype]
-  return (e > TOL[dtype]).mean() <= 0.05 and np.median(e) < 0.3 * TOL[dtype]
+  return np.sqrt((d * d).mean(-1)) / np.sqrt((r * r).mean(-1) + 1e-30)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("seed", range(8))
 def test_models_drawn_at_random(seed, dtype):
-  """whole prompts (one long enough for the tensor-core kernels next to a short one), then decoding together across block edges"""
+  """whole prompts (one long enough for the tensor-core kernels next to a short one), then decoding together across block edges,
+  then a portion.  float32: every row within the tolerance.  bfloat16: a few rows may leave it when two router scores lie closer
+  than the rounding of the router's input (another expert is then chosen legitimately) — but only a few of all rows, and the
+  typical row stays tight."""
   cfg = random_model(seed)
   W = bo.random_weights(cfg, 100 + seed)
   n = make_engine(cfg, W, dtype, max_tokens=800, max_requests=3, page_size=16)
   a, b = rand_tokens(cfg["vocab"], 180, seed), rand_tokens(cfg["vocab"], 30, seed + 50)
   ra, rb = oracle_logits(cfg, W, a)[0], oracle_logits(cfg, W, b)[0]
+  errs = []
   lg, _ = n.step([2, 0], [a[:140], b[:9]], want=list(range(149)))
-  assert rows_ok(lg[:140], ra[:140], dtype) and rows_ok(lg[140:], rb[:9], dtype), json.dumps(cfg["layers"])
-  got_a, got_b = [], []
+  errs += [row_errors(lg[:140], ra[:140]), row_errors(lg[140:], rb[:9])]
   for t in range(21):
     lg, _ = n.step([0, 2], [b[9 + t:10 + t], a[140 + t:141 + t]])
-    got_b.append(lg[0])
-    got_a.append(lg[1])
-  assert rows_ok(np.stack(got_a), ra[140:161], dtype) and rows_ok(np.stack(got_b), rb[9:30], dtype), json.dumps(cfg["layers"])
+    errs += [row_errors(lg[:1], rb[9 + t:10 + t]), row_errors(lg[1:], ra[140 + t:141 + t])]
   lg, _ = n.step([2], [a[161:]], want=list(range(19)))               # a portion of 19 rows after decoding
-  assert rows_ok(lg, ra[161:], dtype)
+  errs.append(row_errors(lg, ra[161:]))
+  e = np.concatenate(errs)
   n.close()
+  if dtype == "float32":
+    assert e.max() < TOL[dtype], json.dumps(cfg["layers"])
+  else:
+    assert (e > TOL[dtype]).mean() <= 0.05 and np.median(e) < 0.3 * TOL[dtype], f"{(e > TOL[dtype]).sum()} of {e.size} rows: " + json.dumps(cfg["layers"])
