@@ -1,6 +1,7 @@
 // layered_kernels.cuh — device code of the layered-model engine (libxotb200_lm.so): decoder models given as a LIST of layers,
 // each a token mixer (latent attention over a paged latent cache, or a generalised delta-rule recurrence over a per-request
-// state) and an optional feed-forward, with grouped RMS norms before and after every sublayer.
+// state) and an optional feed-forward, with grouped RMS norms before and after every sublayer.  The products, the recurrence
+// and the small helpers here also serve the mixers and block forms of layered_gqa.cuh and layered_blocks.cuh.
 //
 // Number formats: every kernel is a template over T, the storage type of weights, GEMM inputs and the latent cache
 // (__nv_bfloat16 when serving, float for the all-32-bit mode).  Whatever T is, these are fp32: the residual stream, every norm,

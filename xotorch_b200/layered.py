@@ -1,11 +1,11 @@
 """`LayeredShard` — synchronous Python owner of one `xotb200_lm*` (include/xotb200_lm.h): models given as a list of layers whose
-token mixers differ (latent attention, delta-rule recurrence) and keep different per-request state.  It offers the methods the
+token mixers differ (latent attention, attention over a key/value cache, delta-rule recurrences) and keep different per-request state.  It offers the methods the
 rest of the package uses on `NativeShard` (`load_dir / begin_request / begin_batch / select_request / clear_request / forward /
 last_token / close / kernel_launches / weight_bytes`) plus the batched `step`, so `B200ShardInferenceEngine`, the Cheetah
 service and the schedulers drive it unchanged.  All compute is in libxotb200_lm.so; there is no CPU fallback.
 
-A model family is a function config.json -> list of `LayerSpec` (see `zokuvik_layers`): the library knows mechanisms and their
-parameters, not families."""
+A model family is a function config.json -> list of `LayerSpec` (see `zokuvik_layers`, `bufulorn_layers`): the library knows
+mechanisms and their parameters, not families."""
 from __future__ import annotations
 
 import ctypes as C
