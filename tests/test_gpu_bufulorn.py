@@ -441,6 +441,17 @@ def test_prompt_kernels_on_aligned_sizes_equal_the_plain_ones():
   assert n.tensor_core_launches() > before
   tc_a = np.concatenate([lg1[:200], lg2])
   assert row_err(tc_a, ra) < TOL["bfloat16"] and row_err(lg1[200:], rb) < TOL["bfloat16"]
+  # three requests decode together: grouped expert products inside decode steps that are captured and replayed as CUDA graphs
+  c = rand_tokens(cfg["vocab"], 12, 11)
+  n.step([2], [c[:4]])
+  a2, b2 = np.concatenate([a, a[:8]]), np.concatenate([b, b[:8]])
+  ra2, rb2, rc = oracle_logits(cfg, W, a2)[0], oracle_logits(cfg, W, b2)[0], oracle_logits(cfg, W, c)[0]
+  replays = n.graph_replays()
+  for t in range(8):
+    lg, _ = n.step([0, 1, 2], [a2[300 + t:301 + t], b2[150 + t:151 + t], c[4 + t:5 + t]])
+    assert row_err(lg, np.stack([ra2[300 + t], rb2[150 + t], rc[4 + t]])) < TOL["bfloat16"], f"decoded token {t}"
+  assert n.graph_replays() - replays >= 5
+  n.clear_request(2)
   n.set_gemm_mode(1)
   n.set_attention_mode(1)
   fma = run_cut(n, 2, a, [200, 100])

@@ -465,7 +465,8 @@ static int launch_ltc(xotb200_lm* e, const CUtensorMap& ma, const CUtensorMap& m
   constexpr int NS = 3;
   auto kern = ltc_gemm_kernel<NT, EPI, NS, TC>;
   CK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ltc_smem_bytes(NT, NS)));
-  kern<<<dim3(cdiv(a.M, LTC_M), cdiv(a.N, NT), batch), LTC_THREADS, ltc_smem_bytes(NT, NS), e->stream>>>(ma, mb, a);
+  const dim3 grid = a.cols_first ? dim3(cdiv(a.N, NT), cdiv(a.M, LTC_M), batch) : dim3(cdiv(a.M, LTC_M), cdiv(a.N, NT), batch);
+  kern<<<grid, LTC_THREADS, ltc_smem_bytes(NT, NS), e->stream>>>(ma, mb, a);
   CK(cudaGetLastError());
   e->launches++;
   e->tc_launches++;
@@ -479,7 +480,7 @@ static int product_tc(xotb200_lm* e, const bf16* A, long lda, long a_batch, cons
   const int nt = (N > 64 && M > LTC_M) ? 128 : 64;   // one row tile: narrower column tiles, twice the CTAs streaming weights
   CUtensorMap ma, mb;
   if (!make_map3(&ma, A, M, K, lda, a_batch, batch, LTC_M) || !make_map3(&mb, B, N, K, ldb, b_batch, batch, nt)) return 0;
-  LtcArgs a{M, N, K, C, ldc, c_batch, e->d_err, static_cast<const bf16*>(epi), nullptr};
+  LtcArgs a{M, N, K, C, ldc, c_batch, e->d_err, static_cast<const bf16*>(epi), nullptr, 0};
   if (nt == 128) TRY((launch_ltc<128, EPI, TC>(e, ma, mb, a, batch)));
   else TRY((launch_ltc<64, EPI, TC>(e, ma, mb, a, batch)));
   return 1;
@@ -939,14 +940,15 @@ static int grouped_product(xotb200_lm* e, const bf16* A, long lda, const bf16* B
   const int nt = N > 64 ? 128 : 64;
   CUtensorMap ma, mb;
   if (!make_map3(&ma, A, m_pad, K, lda, 0, 1, LTC_M) || !make_map3(&mb, B, N, K, ldb, b_batch, n_batch, nt)) return 0;
-  LtcArgs a{m_pad, N, K, C, ldc, 0, e->d_err, nullptr, tile_batch};
+  LtcArgs a{m_pad, N, K, C, ldc, 0, e->d_err, nullptr, tile_batch, 1};
   if (nt == 128) TRY((launch_ltc<128, EPI, TC>(e, ma, mb, a, 1)));
   else TRY((launch_ltc<64, EPI, TC>(e, ma, mb, a, 1)));
   return 1;
 }
 
-// rows from which the experts run as grouped tensor-core products (below: every (row, expert) pair streams its expert)
-static const int MOE_GROUPED_MIN_ROWS = 17;
+// Rows from which the experts run as grouped tensor-core products (below: every (row, expert) pair streams its expert).  Measured
+// on decode batches: from 4 rows on the grouped form is faster (each chosen expert is streamed once, however many rows chose it).
+static const int MOE_GROUPED_MIN_ROWS = 3;
 
 static bool layer_has_ff(const xotb200_lm_layer& s) { return s.ff_kind == XOTB200_LM_FF_MOE ? s.experts > 0 : s.ff > 0; }
 

@@ -41,6 +41,8 @@ struct LtcArgs {
   int* err;
   const __nv_bfloat16* epi;   // EPI 2: the two raw xIELU parameters
   const int* tile_batch;      // not NULL: row tile t reads B's batch tile_batch[t] (A and C are not batched); a negative entry = the tile is empty
+  int cols_first;             // 1: blockIdx.x walks the column tiles and blockIdx.y the row tiles (CTAs that run together share few row tiles:
+                              // a grouped product then streams an expert's matrix while only that expert's rows are in flight)
 };
 
 template <typename TC>
@@ -61,9 +63,10 @@ ltc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   uint64_t* tmem_full = empty + NS;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full + 1);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.x * LTC_M, n0 = blockIdx.y * NT, z = blockIdx.z;
+  const int mt = a.cols_first ? blockIdx.y : blockIdx.x, ntile = a.cols_first ? blockIdx.x : blockIdx.y;
+  const int m0 = mt * LTC_M, n0 = ntile * NT, z = blockIdx.z;
   const int nkb = (a.K + LTC_BK - 1) / LTC_BK;
-  const int zb = a.tile_batch ? a.tile_batch[blockIdx.x] : z;
+  const int zb = a.tile_batch ? a.tile_batch[mt] : z;
   if (zb < 0) return;                                  // an empty tile of a grouped product: the whole CTA leaves before anything is set up
 
   if (threadIdx.x == 0) {
