@@ -768,14 +768,23 @@ static int launch_delta(xotb200_lm* e, LmLayer& L, const StepPlan& sp, DeltaSrc 
   e->launches++;
   return 0;
 }
-// the recurrence is bound by the instructions one warp issues per token (measured: ~2.8 cycles each): key rows over 8 lanes,
-// few columns per thread, four warps per block.  The variant is chosen by the larger of the key and value sizes.
+// The recurrence is bound by the instructions one warp issues per token (measured: ~2.8 cycles each with one warp per scheduler):
+// key rows over 4 or 8 lanes, few columns per thread, four warps per block.  The variant is chosen by the larger of the key and
+// value sizes; of the columns-per-thread choices the widest that still gives CTAs for three quarters of the SMs (a single prompt has only
+// heads x column groups CTAs: narrower threads mean more CTAs and more warps per scheduler to hide the dependent latency).
 static int run_delta(xotb200_lm* e, LmLayer& L, const StepPlan& sp, DeltaSrc ks, DeltaSrc rs, DeltaSrc vs) {
   const int d = std::max(L.s.dim, L.s.vdim);
+  auto fills = [&](int P, int NC) {                    // CTAs of a variant against the SMs
+    const int cpw = (32 / P) * NC, warps = std::max(1, std::min(4, cdiv(L.s.vdim, cpw)));
+    return 4L * sp.n_seq * L.s.heads * cdiv(L.s.vdim, warps * cpw) >= 3L * e->sm_count;
+  };
   if (d <= 16) return launch_delta<4, 4, 2>(e, L, sp, ks, rs, vs);
-  if (d <= 32) return launch_delta<8, 4, 2>(e, L, sp, ks, rs, vs);
-  if (d <= 64) return launch_delta<8, 8, 4>(e, L, sp, ks, rs, vs);
-  if (d <= 128) return launch_delta<16, 8, 2>(e, L, sp, ks, rs, vs);
+  if (d <= 32) return fills(4, 2) ? launch_delta<8, 4, 2>(e, L, sp, ks, rs, vs) : launch_delta<8, 4, 1>(e, L, sp, ks, rs, vs);
+  if (d <= 64)
+    return fills(8, 4) ? launch_delta<8, 8, 4>(e, L, sp, ks, rs, vs)
+         : fills(8, 2) ? launch_delta<8, 8, 2>(e, L, sp, ks, rs, vs)
+                       : launch_delta<8, 8, 1>(e, L, sp, ks, rs, vs);
+  if (d <= 128) return fills(8, 2) ? launch_delta<16, 8, 2>(e, L, sp, ks, rs, vs) : launch_delta<16, 8, 1>(e, L, sp, ks, rs, vs);
   return launch_delta<32, 8, 1>(e, L, sp, ks, rs, vs);
 }
 

@@ -420,21 +420,29 @@ __global__ void delta_rule_kernel(DeltaSrc ksrc, DeltaSrc rsrc, DeltaSrc vsrc, c
   for (int e = threadIdx.x; e < 2 * CH * 6 * DKP; e += blockDim.x) (&buf[0][0][0][0])[e] = 0.f;   // the padding stays zero
   __syncthreads();
   const int HD = H * dk;
+  // A thread copies the same pieces (vector, offset) of every token of a chunk: which pieces is worked out per piece, not per copy
+  // (the divisions stay out of the token loop), and the token loop only adds the source's row stride.
+  const int perk = vec4 ? dk / 4 : dk, perv = vec4 ? dv / 4 : dv;   // copies per key-sized vector / per value vector
+  const int per_tok = 5 * perk + perv;
   auto issue = [&](int c) {
     const int t0 = c * CH, nt = min(CH, sq.n_rows - t0);
-    const int perk = vec4 ? dk / 4 : dk, perv = vec4 ? dv / 4 : dv;   // copies per key-sized vector / per value vector
-    const int per_tok = 5 * perk + perv;
-    for (int e = threadIdx.x; e < nt * per_tok; e += blockDim.x) {
-      const int t = e / per_tok, rem = e % per_tok, vec = rem / perk < 5 ? rem / perk : 5, i = (rem - vec * perk) * (vec4 ? 4 : 1);
-      const size_t m = (size_t)sq.row0 + t0 + t;
-      const float* src = vec == 0 ? wdec + m * HD + h * dk + i
-                       : vec == 1 ? auvec + m * HD + h * dk + i
-                       : vec == 2 ? uvec + m * HD + h * dk + i
-                       : vec == 3 ? ksrc.p + m * ksrc.ld + ksrc.col + h * dk + i
-                       : vec == 4 ? rsrc.p + m * rsrc.ld + rsrc.col + h * dk + i
-                                  : vsrc.p + m * vsrc.ld + vsrc.col + h * dv + i;
-      if (vec4) cp_async16(&buf[c & 1][t][vec][i], src);
-      else cp_async4(&buf[c & 1][t][vec][i], src);
+    const size_t m0 = (size_t)sq.row0 + t0;
+    for (int piece = threadIdx.x; piece < per_tok; piece += blockDim.x) {
+      const int vec = piece / perk < 5 ? piece / perk : 5, i = (piece - vec * perk) * (vec4 ? 4 : 1);
+      const float* src;
+      size_t stride;
+      if (vec == 0) { src = wdec + m0 * HD + h * dk + i; stride = HD; }
+      else if (vec == 1) { src = auvec + m0 * HD + h * dk + i; stride = HD; }
+      else if (vec == 2) { src = uvec + m0 * HD + h * dk + i; stride = HD; }
+      else if (vec == 3) { src = ksrc.p + m0 * ksrc.ld + ksrc.col + h * dk + i; stride = ksrc.ld; }
+      else if (vec == 4) { src = rsrc.p + m0 * rsrc.ld + rsrc.col + h * dk + i; stride = rsrc.ld; }
+      else { src = vsrc.p + m0 * vsrc.ld + vsrc.col + h * dv + i; stride = vsrc.ld; }
+      float* dst = &buf[c & 1][0][vec][i];
+      if (vec4) {
+        for (int t = 0; t < nt; ++t) cp_async16(dst + (size_t)t * 6 * DKP, src + t * stride);
+      } else {
+        for (int t = 0; t < nt; ++t) cp_async4(dst + (size_t)t * 6 * DKP, src + t * stride);
+      }
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
