@@ -97,3 +97,15 @@ def test_oracle_activation_is_continuous_and_matches_its_formula():
   assert abs(float(y[4]) - (sp(p) * 2.25 + 0.75)) < 1e-6
   assert abs(float(y[0]) - ((0.5 + sp(q)) * (math.exp(-2.0) - 1 + 2.0) - 1.0)) < 1e-6
   assert abs(float(y[1])) < 1e-5 and float(y[2]) == 0.0 and abs(float(y[3])) < 1e-5
+
+
+def test_batch_scheduler_refuses_requests_beyond_the_position_table():
+  from tests.test_layered_host_logic import FakeLayered, fake_generate
+  from xotorch_b200.scheduler import ContinuousBatch
+  n = FakeLayered()
+  n.max_positions = 20
+  s = ContinuousBatch(n, max_requests=2, max_tokens=64, page_size=8)
+  with pytest.raises(ValueError, match="positions"):
+    s.submit("long", list(range(1, 16)), 7)           # 15 + 7 - 1 = 21 tokens would be held
+  s.submit("fits", list(range(1, 16)), 6)             # 20 tokens held: the last generated token is never fed back
+  assert s.run_until_idle()["fits"] == fake_generate(list(range(1, 16)), 6)

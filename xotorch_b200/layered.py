@@ -209,6 +209,10 @@ class LayeredShard:
   def vocab(self) -> int: return self.globals["vocab"]
   @property
   def width(self) -> int: return self.globals["width"]
+  @property
+  def max_positions(self) -> int:
+    """most tokens a request may hold (a learned position table ends there); 0 = no such limit"""
+    return int(self.globals.get("max_positions", 0))
 
   def set_shard(self, start_layer: int, end_layer: int, shapes: Dict[str, Tuple[int, ...]]):
     """create the native engine for layers [start_layer, end_layer]; `shapes` = tensor name -> shape (sizes that only a

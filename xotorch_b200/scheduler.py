@@ -225,6 +225,9 @@ class ContinuousBatch:
       raise ValueError("a request needs at least one prompt token and one token to generate")
     if p.shape[1] + max_tokens > self.max_tokens:
       raise ValueError(f"request {request_id!r}: {p.shape[1]} prompt + {max_tokens} generated tokens exceed the cache of {self.max_tokens} tokens")
+    limit = int(getattr(self.engines[0], "max_positions", 0) or 0)    # a model with a position table cannot go past its end
+    if limit and p.shape[1] + max_tokens - 1 > limit:
+      raise ValueError(f"request {request_id!r}: {p.shape[1]} prompt + {max_tokens} generated tokens exceed the model's {limit} positions")
     with self._lock:
       self.waiting.append(_Req(request_id, p, int(max_tokens), eos_token_id))
 
